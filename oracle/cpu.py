@@ -30,9 +30,10 @@ def build(force=False):
     if force or not os.path.exists(_LIB_PATH):
         subprocess.check_call(["make", "-C", _HERE, "oracle"], stdout=subprocess.DEVNULL)
     ref_so = os.path.join(_HERE, "_ref", "libref_cpu.so")
-    if os.path.isdir("/root/reference") and (force or not os.path.exists(ref_so)):
+    have_ref = os.path.exists("/root/reference/attention_cpu/int8_quant.cpp")    # an empty folder is no reference
+    if have_ref and (force or not os.path.exists(ref_so)):
         subprocess.check_call(["make", "-C", _HERE, "ref"], stdout=subprocess.DEVNULL)
-    if os.path.isdir("/root/reference"):
+    if have_ref:
         # the reference's own cpu_paged_attention_forward<float> + decoder headers (oracle/_ref/libref_attn.so)
         from . import build_ref_attention
         build_ref_attention.build(force=force)

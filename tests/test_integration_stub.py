@@ -32,7 +32,7 @@ def test_stub_compiles_and_links(tmp_path):
 
 
 def test_mirror_matches_reference_headers():
-    if not os.path.isdir("/root/reference"):
+    if not os.path.exists("/root/reference/kv_cache/page_table.hpp"):
         pytest.skip("no /root/reference")
     mirror = open(MIRROR).read()
     for hdr, cls in (("kv_cache/page_table.hpp", "PageTable"), ("kv_cache/kv_tile_cache.hpp", "KVTileCache")):
