@@ -698,6 +698,72 @@ int pa_latent_attention(const void* d_q_lat, int64_t ql_row_stride, int64_t ql_h
                         int64_t o_row_stride, int64_t o_head_stride, int elem, int nsplit, int tile_kind,
                         void* d_workspace, size_t workspace_bytes, pa_stream_t stream);
 
+/* ---- pre-norm wiring, looped blocks (seq_ops.cu) ---------------------------------------------------------------------
+ * pa_residual_add_prenorm: x[r] += y_scale * y + y2_scale * y2 + sum_k sel_w[r, k] * routed[(r, k)] + shared + bias
+ *   (every addend optional; y, y2, shared in the activation type, routed float pairs, bias one float row), then, when
+ *   d_next is given, next[r] = x[r] / sqrt(mean(x[r]^2) + eps) * d_gain in the activation type.
+ * pa_concat_rows: out[r] = [a[r] | b[r]] (two float row sets of equal width) in the activation type.
+ * pa_router_topk_grouped: pa_router_topk where the experts form `ngroups` equal groups of neighbours and only experts
+ *   of the `keep` groups with the largest maxima can be chosen. */
+int pa_residual_add_prenorm(float* d_x, int64_t rows, int width, const void* d_y, float y_scale, const void* d_y2,
+                            float y2_scale, const float* d_routed, const float* d_sel_w, int top, const void* d_shared,
+                            const float* d_bias, float eps, const float* d_gain, void* d_next, int elem,
+                            pa_stream_t stream);
+int pa_concat_rows(const float* d_a, const float* d_b, int64_t rows, int width, void* d_out, int elem,
+                   pa_stream_t stream);
+int pa_router_topk_grouped(const void* d_h, const float* d_w_router, const float* d_bias, const float* d_w_shared_gate,
+                           int rows, int width, int experts, int top, int score_fn, int renorm, int ngroups, int keep,
+                           int32_t* d_sel_id, float* d_sel_w, float* d_shared_gate, int elem, pa_stream_t stream);
+
+/* ---- softmax attention with score modifiers and visibility rules (masked_attention.cu) ------------------------------
+ * Grouped key/value heads over the pools pa_kv_append_rows fills (key rows of `dim`, value rows of `vdim`), no rotation.
+ * score = (q . k) * scale; softcap > 0: softcap * tanh(score / softcap); bias_kind 1: - d_bias[h] * (i - j);
+ * bias_kind 2: + d_bias[min(i - j, bias_len - 1) * heads + h].  mask_kind 0: causal; 1: 0 <= i - j < mask_size;
+ * 2: j <= i in the same block of mask_size positions (blocks counted from position 0 of the sequence).
+ * d_q_tiles as for pa_diff_attention: runs of at most pa_masked_attention_tile_tokens(heads, kv_heads) tokens
+ * (tile_kind 0 or 1: the float kernels, any shape, both element types), or of at most
+ * pa_masked_attention_mma_tile_tokens(dim, vdim, elem) tokens (tile_kind 2: bfloat16 on the tensor cores; 0 = not
+ * served; PA_ERR_UNSUPPORTED where a stride or an alignment rules it out). */
+int pa_masked_attention_tile_tokens(int heads, int kv_heads);
+int pa_masked_attention_mma_tile_tokens(int dim, int vdim, int elem);
+int pa_masked_attention(const void* d_q, int64_t q_stride, int q_off, const void* d_k_pool, const void* d_v_pool,
+                        const int32_t* d_table, int num_slots, int num_kv_heads, int num_tiles, int total_pages,
+                        int tile_size, const int32_t* d_q_tiles, int num_q_tiles, int heads, int dim, int vdim,
+                        float scale, float softcap, int mask_kind, int mask_size, int bias_kind, const float* d_bias,
+                        int bias_len, void* d_out, int elem, int tile_kind, pa_stream_t stream);
+
+/* ---- matrix-state recurrences (recurrence_ops.cu) --------------------------------------------------------------------
+ * pa_causal_conv_silu: out[r, c] = silu(bias[c] + sum_i w[c, i] * in(t - (taps - 1 - i))[c]) over the tokens of a
+ *   sequence (weights [channels][taps], taps <= 8); inputs before a portion's first token come from the state slot
+ *   [slots][taps - 1][channels] (float).  d_chunks [num_chunks][4] = (first row, tokens, slot, offset of the first token
+ *   within its portion).  pa_conv_state_update then leaves the portion's last taps - 1 inputs in the slot.
+ * pa_decay_scan: per head S_t = a_t S_{t-1} + k_t (s_t v_t)^T, o_t = S_t^T q_t + skip[h] * v_t, S [dim][vdim] float in
+ *   d_state [slots][heads][dim][vdim].  q / k of head h are read at off + (h / (heads / groups)) * dim, v at
+ *   off + h * vdim; act 1: q, k, v pass silu.  d_dt == NULL: a_t = d_decay[h], s_t = 1.  Else dt = softplus(raw + d_dt_bias[h])
+ *   (raw at dt_off + h), a_t = exp(-exp(d_a_log[h]) * dt), s_t = dt.  d_out: float rows [heads * vdim].
+ *   chunked 0: d_items [num_items][4] = one item per portion (first row, tokens, slot, -), walked in order from / to the
+ *   slot.  chunked 1: items are chunks of portions in portion order, d_seq_chunk0 / d_seq_nchunks / d_seq_slot describe
+ *   the portions; three passes (fold, chain, replay) with pa_decay_scan_workspace_bytes(num_items, ...) of workspace.
+ * pa_gated_rms_norm: out[r] = RMS norm of the float row y[r] in `groups` equal parts (each by its own mean square)
+ *   times d_weight; gate_mode 1: y is first multiplied by silu(gate); gate_mode 2: the result by sigmoid(gate). */
+int pa_causal_conv_silu(const void* d_in, int64_t in_stride, int in_off, int channels, int taps, const float* d_weight,
+                        const float* d_bias, const float* d_state, const int32_t* d_chunks, int num_chunks, void* d_out,
+                        int64_t out_stride, int elem, pa_stream_t stream);
+int pa_conv_state_update(const void* d_in, int64_t in_stride, int in_off, int channels, int taps,
+                         const int32_t* d_seq_start, const int32_t* d_seq_len, const int32_t* d_seq_slot, int num_seqs,
+                         float* d_state, int elem, pa_stream_t stream);
+size_t pa_decay_scan_workspace_bytes(int num_chunks, int heads, int dim, int vdim);
+int pa_decay_scan(const void* d_q, int64_t q_stride, int q_off, const void* d_k, int64_t k_stride, int k_off,
+                  const void* d_v, int64_t v_stride, int v_off, int heads, int groups, int dim, int vdim, int act,
+                  const float* d_decay, const void* d_dt, int64_t dt_stride, int dt_off, const float* d_dt_bias,
+                  const float* d_a_log, const float* d_skip, float* d_state, float* d_out, int64_t out_stride,
+                  const int32_t* d_items, int num_items, const int32_t* d_seq_chunk0, const int32_t* d_seq_nchunks,
+                  const int32_t* d_seq_slot, int num_seqs, int chunked, void* d_workspace, size_t workspace_bytes,
+                  int elem, pa_stream_t stream);
+int pa_gated_rms_norm(const float* d_y, int64_t rows, int inner, int groups, const void* d_gate, int64_t gate_stride,
+                      int gate_off, int gate_mode, const float* d_weight, float eps, void* d_out, int elem,
+                      pa_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,7 +6,7 @@ The .so lands next to csrc/ (git-ignored, but it travels to the GPU box with gpu
 
 --core builds libpa_b200_core.so from the CORE sources only: the page table, the small decoder ops with the fp32 linear
 layer, sampling, and the ragged-batch sequence ops (norm / token shift / recurrence, differential and latent attention,
-routed experts).  It is what the config-driven models need; a first run in a fresh checkout compiles this and no more.
+routed experts, masked softmax attention, matrix-state recurrences).  It is what the config-driven models need; a first run in a fresh checkout compiles this and no more.
 """
 import glob
 import os
@@ -19,7 +19,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libpa_b200.so")
 OUT_CORE = os.path.join(HERE, "libpa_b200_core.so")
 CORE = ("page_table.cu", "decoder_ops.cu", "linear_tf32x3.cu", "sampling.cu", "seq_ops.cu", "diff_attention.cu",
-        "latent_attention.cu", "moe_ops.cu")
+        "latent_attention.cu", "masked_attention.cu", "recurrence_ops.cu", "moe_ops.cu")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
 FLAGS = [

@@ -19,7 +19,9 @@ namespace pa {
 
 // ---- router ---------------------------------------------------------------------------------------------------------
 // One warp per row.  score_fn: 0 = sigmoid, 1 = softmax over the experts, 2 = the largest LOGITS are chosen and the
-// weights are the softmax over the chosen logits only.  Ties go to the lower expert id.
+// weights are the softmax over the chosen logits only.  Ties go to the lower expert id.  With ngroups > 1 the experts
+// form ngroups equal groups of neighbours, a group's score is its largest score, and only experts of the `keep` best
+// groups (ties: lower group) can be chosen.
 // The dot products run over groups of kRtGroup weight vectors (the experts' rows and, last, the shared-expert gate's):
 // a lane takes 16-byte pieces of the token row and multiplies each into the whole group, so the row is read once per
 // group and the weights with 16-byte loads (VEC; rows whose width or alignment does not allow it go element by element).
@@ -45,7 +47,7 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const T* __restrict__ 
                                                           const float* __restrict__ bias,
                                                           const float* __restrict__ w_shared_gate, int rows, int width,
                                                           int experts, int top, int score_fn, int renorm,
-                                                          int32_t* __restrict__ sel_id, float* __restrict__ sel_w,
+                                                          int ngroups, int keep, int32_t* __restrict__ sel_id, float* __restrict__ sel_w,
                                                           float* __restrict__ shared_gate) {
     extern __shared__ float sc[];                     // [warps][experts]
     constexpr int VN = 16 / sizeof(T);
@@ -109,6 +111,23 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const T* __restrict__ 
             for (int e = 0; e < experts; ++e) m = fmaxf(m, s[e]);
             for (int e = 0; e < experts; ++e) { s[e] = expf(s[e] - m); z += s[e]; }
             for (int e = 0; e < experts; ++e) s[e] /= z;
+        }
+        if (ngroups > 1 && keep < ngroups) {          // only the experts of the `keep` groups with the largest maxima stay
+            const int gsz = experts / ngroups;
+            unsigned long long kept = 0ull;           // ngroups <= 64
+            for (int k = 0; k < keep; ++k) {
+                int bg = -1;
+                float bv = -INFINITY;
+                for (int gi = 0; gi < ngroups; ++gi) {
+                    if (kept >> gi & 1ull) continue;
+                    float gm = -INFINITY;
+                    for (int e = gi * gsz; e < (gi + 1) * gsz; ++e) gm = fmaxf(gm, s[e]);
+                    if (bg < 0 || gm > bv) { bv = gm; bg = gi; }
+                }
+                kept |= 1ull << bg;
+            }
+            for (int e = 0; e < experts; ++e)
+                if (!(kept >> (e / gsz) & 1ull)) s[e] = -INFINITY;
         }
         float total = 0.f;
         for (int k = 0; k < top; ++k) {
@@ -588,10 +607,13 @@ static bool mma_ok(const void* A, int64_t lda, const void* W, int K) {
 
 using namespace pa;
 
-PA_API int pa_router_topk(const void* d_h, const float* d_w_router, const float* d_bias, const float* d_w_shared_gate,
-                          int rows, int width, int experts, int top, int score_fn, int renorm, int32_t* d_sel_id,
-                          float* d_sel_w, float* d_shared_gate, int elem, pa_stream_t stream) {
+PA_API int pa_router_topk_grouped(const void* d_h, const float* d_w_router, const float* d_bias,
+                                  const float* d_w_shared_gate, int rows, int width, int experts, int top, int score_fn,
+                                  int renorm, int ngroups, int keep, int32_t* d_sel_id, float* d_sel_w,
+                                  float* d_shared_gate, int elem, pa_stream_t stream) {
     PA_CHECK_ARG(d_h && d_w_router && d_sel_id && d_sel_w && rows >= 0 && width > 0 && experts > 0);
+    PA_CHECK_ARG(ngroups >= 1 && ngroups <= 64 && experts % ngroups == 0 && keep >= 1 && keep <= ngroups);
+    PA_CHECK_ARG((int64_t)keep * (experts / ngroups) >= top);
     PA_CHECK_ARG(top > 0 && top <= experts && score_fn >= 0 && score_fn <= 2 && (!d_w_shared_gate || d_shared_gate));
     if (rows == 0) return PA_OK;
     if (experts > 2048) return PA_ERR_UNSUPPORTED;
@@ -602,11 +624,18 @@ PA_API int pa_router_topk(const void* d_h, const float* d_w_router, const float*
 #define PA_ROUTER(VEC)                                                                                                 \
     PA_DISPATCH_ELEM(elem, (router_topk_kernel<T, VEC><<<(unsigned)((rows + 3) / 4), 128, smem, as_stream(stream)>>>(  \
                                static_cast<const T*>(d_h), d_w_router, d_bias, d_w_shared_gate, rows, width, experts, top, \
-                               score_fn, renorm, d_sel_id, d_sel_w, d_shared_gate)))
+                               score_fn, renorm, ngroups, keep, d_sel_id, d_sel_w, d_shared_gate)))
     if (vec) PA_ROUTER(true);
     else PA_ROUTER(false);
 #undef PA_ROUTER
     PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_router_topk(const void* d_h, const float* d_w_router, const float* d_bias, const float* d_w_shared_gate,
+                          int rows, int width, int experts, int top, int score_fn, int renorm, int32_t* d_sel_id,
+                          float* d_sel_w, float* d_shared_gate, int elem, pa_stream_t stream) {
+    return pa_router_topk_grouped(d_h, d_w_router, d_bias, d_w_shared_gate, rows, width, experts, top, score_fn, renorm, 1,
+                                  1, d_sel_id, d_sel_w, d_shared_gate, elem, stream);
 }
 
 PA_API int pa_moe_tile_rows(void) { return kGlBM; }

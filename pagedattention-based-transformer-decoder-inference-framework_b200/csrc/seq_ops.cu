@@ -13,6 +13,10 @@
 //   residual_combine_kernel   x += m * (mixer + dense ff + sum of routed expert rows + gate * shared expert)
 //   residual_add_norm_kernel  x += rms_norm(y + sum_k w_k * routed expert rows) * gain  (norm on the sublayer's OUTPUT),
 //                             optionally leaving the new x in the activation type for the next sublayer's products
+//   residual_add_prenorm_kernel  x += a * y + b * y2 + sum_k w_k * routed expert rows + shared + bias, then the NEXT
+//                             sublayer's operand h = x / rms(x) * gain in the activation type (pre-norm wiring: the
+//                             residual add of one sublayer fused with the norm in front of the next)
+//   concat_rows_kernel        [x | x0] of two float row sets in the activation type (input of a looped block)
 //
 // Norms, the recurrence with its gates, and the residual sum are computed in float whatever the activation type.
 #include "seq_common.cuh"
@@ -362,6 +366,48 @@ __global__ void __launch_bounds__(256) residual_add_norm_kernel(float* __restric
     }
 }
 
+// One CTA per row.  Every addend is optional; `next` (with `gain`) is left out after the last sublayer.
+template <typename T>
+__global__ void __launch_bounds__(256) residual_add_prenorm_kernel(float* __restrict__ x, int width, const T* __restrict__ y,
+                                                                   float y_scale, const T* __restrict__ y2, float y2_scale,
+                                                                   const float* __restrict__ routed,
+                                                                   const float* __restrict__ sel_w, int top,
+                                                                   const T* __restrict__ shared, const float* __restrict__ bias,
+                                                                   float eps, const float* __restrict__ gain,
+                                                                   T* __restrict__ next) {
+    extern __shared__ float row[];                    // [width]
+    __shared__ float sm[32];
+    const int64_t r = blockIdx.x;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float s = 0.f;
+        if (y) s = y_scale * to_f32<T>(y[r * width + j]);
+        if (y2) s = fmaf(y2_scale, to_f32<T>(y2[r * width + j]), s);
+        if (routed)
+            for (int k = 0; k < top; ++k) s = fmaf(sel_w ? sel_w[r * top + k] : 1.0f, routed[(r * top + k) * width + j], s);
+        if (shared) s += to_f32<T>(shared[r * width + j]);
+        if (bias) s += bias[j];
+        const float v = x[r * width + j] + s;
+        x[r * width + j] = v;
+        row[j] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!next) return;
+    ss = block_sum(ss, sm);
+    const float rn = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int j = threadIdx.x; j < width; j += blockDim.x) next[r * width + j] = from_f32<T>(row[j] * rn * gain[j]);
+}
+
+template <typename T>
+__global__ void concat_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, int64_t rows, int width,
+                                   T* __restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * 2 * width) return;
+    const int64_t r = i / (2 * width);
+    const int j = (int)(i % (2 * width));
+    out[i] = from_f32<T>(j < width ? a[r * width + j] : b[r * width + j - width]);
+}
+
 template <typename T>
 __global__ void cast_rows_kernel(const float* __restrict__ x, int64_t n, T* __restrict__ out) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -506,6 +552,31 @@ PA_API int pa_residual_add_norm(float* d_x, int64_t rows, int width, float eps, 
     PA_DISPATCH_ELEM(elem, residual_add_norm_kernel<T><<<(unsigned)rows, 256, smem, as_stream(stream)>>>(
                                d_x, width, eps, d_gain, static_cast<const T*>(d_y), d_routed, d_sel_w, top,
                                static_cast<T*>(d_next)));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_residual_add_prenorm(float* d_x, int64_t rows, int width, const void* d_y, float y_scale, const void* d_y2,
+                                   float y2_scale, const float* d_routed, const float* d_sel_w, int top,
+                                   const void* d_shared, const float* d_bias, float eps, const float* d_gain, void* d_next,
+                                   int elem, pa_stream_t stream) {
+    PA_CHECK_ARG(d_x && rows >= 0 && width > 0 && (!d_routed || top > 0) && (!d_next || d_gain));
+    if (rows == 0) return PA_OK;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 48 * 1024) return PA_ERR_UNSUPPORTED;
+    PA_DISPATCH_ELEM(elem, residual_add_prenorm_kernel<T><<<(unsigned)rows, 256, smem, as_stream(stream)>>>(
+                               d_x, width, static_cast<const T*>(d_y), y_scale, static_cast<const T*>(d_y2), y2_scale,
+                               d_routed, d_sel_w, top, static_cast<const T*>(d_shared), d_bias, eps, d_gain,
+                               static_cast<T*>(d_next)));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_concat_rows(const float* d_a, const float* d_b, int64_t rows, int width, void* d_out, int elem,
+                          pa_stream_t stream) {
+    PA_CHECK_ARG(d_a && d_b && d_out && rows >= 0 && width > 0);
+    if (rows == 0) return PA_OK;
+    const int64_t n = rows * 2 * width;
+    PA_DISPATCH_ELEM(elem, concat_rows_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(
+                               d_a, d_b, rows, width, static_cast<T*>(d_out)));
     PA_RETURN_LAUNCH_STATUS();
 }
 

@@ -145,6 +145,22 @@ _SIGS = {
     "pa_latent_attention_workspace_bytes": ([_i32, _i32, _i32, _i32], _sz),
     "pa_latent_attention": ([_vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _i32,
                              _f32, _vp, _i64, _i64, _i32, _i32, _i32, _vp, _sz, _vp], _i32),
+    # pre-norm wiring, looped blocks, grouped router
+    "pa_residual_add_prenorm": ([_vp, _i64, _i32, _vp, _f32, _vp, _f32, _vp, _vp, _i32, _vp, _vp, _f32, _vp, _vp, _i32, _vp], _i32),
+    "pa_concat_rows": ([_vp, _vp, _i64, _i32, _vp, _i32, _vp], _i32),
+    "pa_router_topk_grouped": ([_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _vp], _i32),
+    # softmax attention with score modifiers and visibility rules (masked_attention.cu)
+    "pa_masked_attention_tile_tokens": ([_i32, _i32], _i32),
+    "pa_masked_attention_mma_tile_tokens": ([_i32, _i32, _i32], _i32),
+    "pa_masked_attention": ([_vp, _i64, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _i32,
+                             _f32, _f32, _i32, _i32, _i32, _vp, _i32, _vp, _i32, _i32, _vp], _i32),
+    # matrix-state recurrences (recurrence_ops.cu)
+    "pa_causal_conv_silu": ([_vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _i32, _vp], _i32),
+    "pa_conv_state_update": ([_vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _vp, _i32, _vp], _i32),
+    "pa_decay_scan_workspace_bytes": ([_i32, _i32, _i32, _i32], _sz),
+    "pa_decay_scan": ([_vp, _i64, _i32, _vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _i64, _i32,
+                       _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _sz, _i32, _vp], _i32),
+    "pa_gated_rms_norm": ([_vp, _i64, _i32, _i32, _vp, _i64, _i32, _i32, _vp, _f32, _vp, _i32, _vp], _i32),
 }
 
 EXPORTS = tuple(_SIGS)

@@ -1,7 +1,7 @@
 """HybridDecoder -- a config-driven decoder stack over a ragged batch: every layer is one MIXER (picked by the layer's
 `type` from MIXERS) plus an optional FEED-FORWARD (picked by `mlp.kind` from FEED_FORWARDS); the residual stream is
 float.  A DESIGN (config "architecture", table DESIGNS) fixes how a layer is wired and with which constants the
-mechanisms are built.  Two designs are served.
+mechanisms are built.  Three designs are served.
 
 `Megusun` (wiring 'parallel': mixer and feed-forward both read the same pre-norm output):
 
@@ -35,6 +35,23 @@ mechanisms are built.  Two designs are served.
   ff 'moe'           logits W_r h + b, the `top` largest, weights = softmax over the chosen logits, applied to the
                      expert's OUTPUT; experts W_down relu(W_up h)^2
 
+`Dubarax` (wiring 'pre_norm': x += mixer(N1(x)), then x += ff(N2(x)), N(x; w) = x / sqrt(mean(x^2) + eps) * (1 + w)); a
+  block of layers [loop.start, loop.stop) may run loop.times times in a row with the same weights and a cache / state of
+  its own per pass, each pass entered through x <- W_in [x | x0] + step_t (x0: the scaled embedding):
+
+  mixer 'attention'  softmax attention with grouped key/value heads, biased projections, no rotation, tanh soft cap of the
+                     scores, a learned bias over logarithmic distance buckets, and a sliding window (csrc/masked_attention.cu)
+  mixer 'parallel'   two mixers on the same input, a_l * left + a_r * right: left = the same attention kernel with a
+                     per-head linear distance penalty and visibility inside fixed chunks of positions; right = linear
+                     attention with a per-head decay, S_t = d S_{t-1} + k_t v_t^T, o_t = S_t^T q_t on silu(q, k, v), normed
+                     over all heads, gated by sigmoid(W_g h) (csrc/recurrence_ops.cu)
+  mixer 'mamba2'     selective state space layer: one input product [z | x | B | C | dt], causal convolution + silu over
+                     [x | B | C], S_t = exp(-exp(A) dt) S_{t-1} + dt B_t x_t^T, y_t = S_t^T C_t + D x_t, y * silu(z), RMS norm
+                     in groups, output product (same scan kernel as the linear attention)
+  ff 'moe'           softmax router over all experts, experts in groups of neighbours of which only the best `keep`
+                     groups (by their largest score) can be chosen, the `top` largest scores un-renormalised on the
+                     experts' OUTPUT, silu-gated experts, plus an always-on shared expert
+
 Every size and constant comes from config.json (or a tensor's shape); the constants a design fixes are the arguments
 the mechanisms are constructed with.  Two precisions: 'bfloat16' (matrix products and their activations in bfloat16
 with float accumulation; norms, shift, recurrence, softmax, routers and the residual in float) and 'float32'
@@ -43,6 +60,7 @@ with float accumulation; norms, shift, recurrence, softmax, routers and the resi
 All compute is in libpa_b200.so kernels, except the plain bfloat16 matrix products, which go to the vendor GEMM
 (cuBLASLt through torch.nn.functional.linear).  Weight names: '<layer>.mix.*', '<layer>.mlp.*', '<layer>.norm1',
 '<layer>.shift', 'embed', 'final.norm', 'head' (linear weights [out, in])."""
+import copy
 import json
 import math
 import os
@@ -311,6 +329,279 @@ class LatentAttentionMixer:
         return c.model._linear(og, self.w_o)
 
 
+MASK_KIND = {"causal": 0, "window": 1, "chunk": 2}
+CONV_CHUNK = 64           # tokens per work item of the causal convolution
+DECAY_CHUNK = 64          # tokens per chunk of the chunked matrix-state scan
+DECAY_CHUNKED_FROM = 256  # portions at least this long use it
+
+
+def log_distance_bucket(n, buckets, far):
+    """Bucket of distance n >= 0: exact below buckets // 2, then logarithmic steps that reach the last bucket at `far`."""
+    half = buckets // 2
+    if n < half:
+        return n
+    return min(buckets - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (buckets - half))))
+
+
+class MaskedAttention:
+    """Softmax attention with grouped key/value heads and biased projections over a paged pool of its own; the design
+    picks the visibility rule (`mask`: 'causal', 'window' or 'chunk' of cfg mask.size), the distance bias (`bias`: None,
+    'slope' -- minus 2^(-slope_exp (h + 1) / heads) per step of distance -- or 'bucket' -- a learned table '<prefix>rel'
+    [buckets, heads] over log_distance_bucket(distance, buckets, cfg bias_max)) and whether cfg 'softcap' caps the
+    scores.  It reads its q | k | v from a projection buffer at a column offset, so a mixer can fuse its input product
+    with others."""
+
+    def __init__(self, model, prefix, cfg, W, mask="causal", bias=None, softcap=False, slope_exp=8.0):
+        self.heads, self.kv_heads = int(cfg["heads"]), int(cfg["kv_heads"])
+        self.dim, self.vdim = int(cfg["dim"]), int(cfg["vdim"])
+        if self.heads % self.kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.scale = float(cfg["scale"])
+        self.softcap = float(cfg["softcap"]) if softcap else 0.0
+        self.mask_kind = MASK_KIND[mask]
+        self.mask_size = int(cfg["mask"]["size"]) if mask != "causal" else 0
+        H = self.heads
+        shapes = (("q", H * self.dim), ("k", self.kv_heads * self.dim), ("v", self.kv_heads * self.vdim))
+        for name, rows in shapes:
+            if tuple(W[prefix + name].shape) != (rows, model.width) or tuple(W[prefix + name + ".b"].shape) != (rows,):
+                raise ValueError(f"{prefix}{name}: shape does not match the config")
+        if tuple(W[prefix + "o"].shape) != (model.width, H * self.vdim):
+            raise ValueError(f"{prefix}o: shape does not match the config")
+        self.in_weight = torch.cat([W[prefix + n] for n, _ in shapes], 0)
+        self.in_bias = torch.cat([W[prefix + n + ".b"] for n, _ in shapes], 0)
+        self.q_cols, self.k_cols = H * self.dim, self.kv_heads * self.dim
+        self.in_cols = self.q_cols + self.k_cols + self.kv_heads * self.vdim
+        self.w_o, self.b_o = model._weight(W[prefix + "o"]), model._bias(W[prefix + "o.b"])
+        self.bias_kind, self.bias_len, self.bias = 0, 0, None
+        if bias == "slope":
+            self.bias_kind = 1
+            self.bias = model._f32(torch.tensor([2.0 ** (-slope_exp * (h + 1) / H) for h in range(H)], dtype=torch.float64))
+        elif bias == "bucket":
+            rel = W[prefix + "rel"].to(torch.float64)
+            if rel.dim() != 2 or rel.shape[1] != H:
+                raise ValueError(f"{prefix}rel: one column per head expected")
+            B, far = int(rel.shape[0]), float(cfg["bias_max"])
+            # every distance from `far` on falls into the last bucket, and a window never looks further than its size
+            n = int(math.ceil(far)) + 1
+            if self.mask_kind == 1:
+                n = min(n, self.mask_size)
+            idx = torch.tensor([log_distance_bucket(d, B, far) for d in range(max(n, 1))])
+            self.bias_kind, self.bias_len, self.bias = 2, int(idx.numel()), model._f32(rel[idx])
+        elif bias is not None:
+            raise ValueError(f"unknown distance bias {bias!r}")
+        self.tile_tokens = model._lib.pa_masked_attention_tile_tokens(self.heads, self.kv_heads)
+        self.mma_tokens = model._lib.pa_masked_attention_mma_tile_tokens(self.dim, self.vdim, _ELEM[model.act_dtype])
+        self.alloc_state(model)
+
+    def alloc_state(self, model):
+        self.kv = model.states.add_kv_layer(self.kv_heads, self.dim, self.vdim, _KV[model.act_dtype])
+
+    def attend(self, c, proj, off):
+        """proj [R, stride] holds q | k | v of this step's rows from column `off`; appends k / v to the pool and
+        returns the heads' outputs [R, heads * vdim]."""
+        b, lib, kv, s = c.batch, c.lib, self.kv, _cabi.stream()
+        kv.append_rows(proj, off + self.q_cols, off + self.q_cols + self.k_cols, b.row_slot, b.row_pos)
+        out = c.empty(c.R, self.heads * self.vdim)
+        pt = kv.page_table_
+        table = pt.device_data()
+        for kind, group in b.query_tiles(self.tile_tokens, self.mma_tokens, MMA_FROM).items():
+            if group is None:
+                continue
+            tiles, ntiles, _longest = group
+            st = lib.pa_masked_attention(proj.data_ptr(), proj.stride(0), off, kv.key_buffer_.data_ptr(),
+                                         kv.value_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_, pt.num_heads_,
+                                         pt.num_tiles_, kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles,
+                                         self.heads, self.dim, self.vdim, self.scale, self.softcap, self.mask_kind,
+                                         self.mask_size, self.bias_kind, _cabi.ptr(self.bias), self.bias_len,
+                                         out.data_ptr(), c.elem, kind, s)
+            if kind == 2 and st == _cabi.PA_ERR_UNSUPPORTED:    # a stride or an alignment the tensor-core kernel refuses
+                self.mma_tokens = 0
+                return self.attend_tiles_float(c, proj, off, out)
+            _chk(st, "pa_masked_attention")
+        return out
+
+    def attend_tiles_float(self, c, proj, off, out):
+        b, lib, kv, s = c.batch, c.lib, self.kv, _cabi.stream()
+        pt = kv.page_table_
+        table = pt.device_data()
+        for kind, group in b.query_tiles(self.tile_tokens, 0, MMA_FROM).items():
+            if group is None:
+                continue
+            tiles, ntiles, _longest = group
+            _chk(lib.pa_masked_attention(proj.data_ptr(), proj.stride(0), off, kv.key_buffer_.data_ptr(),
+                                         kv.value_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_, pt.num_heads_,
+                                         pt.num_tiles_, kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles,
+                                         self.heads, self.dim, self.vdim, self.scale, self.softcap, self.mask_kind,
+                                         self.mask_size, self.bias_kind, _cabi.ptr(self.bias), self.bias_len,
+                                         out.data_ptr(), c.elem, kind, s), "pa_masked_attention")
+        return out
+
+    def project_out(self, c, heads_out):
+        return c.model._linear(heads_out, self.w_o, bias=self.b_o)
+
+
+def decay_scan(c, state, out, heads, groups, dim, vdim, q, k, v, act=0, decay=None, dt=None, dt_bias=None, a_log=None,
+               skip=None):
+    """The matrix-state recurrence of csrc/recurrence_ops.cu over this step's portions: q, k, v and dt are (buffer,
+    column offset) pairs; long portions take the chunked three-pass form."""
+    b, lib = c.batch, c.lib
+    chunked = max(p[1] for p in b.portions) >= DECAY_CHUNKED_FROM
+    items, n, s0, sn = b.chunk_items(DECAY_CHUNK if chunked else 0)
+    ws = None
+    if chunked:
+        ws = c.empty(lib.pa_decay_scan_workspace_bytes(n, heads, dim, vdim), dtype=torch.uint8)
+    _chk(lib.pa_decay_scan(q[0].data_ptr(), q[0].stride(0), q[1], k[0].data_ptr(), k[0].stride(0), k[1], v[0].data_ptr(),
+                           v[0].stride(0), v[1], heads, groups, dim, vdim, act, _cabi.ptr(decay),
+                           dt[0].data_ptr() if dt else None, dt[0].stride(0) if dt else 0, dt[1] if dt else 0,
+                           _cabi.ptr(dt_bias), _cabi.ptr(a_log), _cabi.ptr(skip), state.data_ptr(), out.data_ptr(),
+                           out.stride(0), items.data_ptr(), n, s0.data_ptr(), sn.data_ptr(), b.seq_slot.data_ptr(),
+                           b.num_seqs, 1 if chunked else 0, _cabi.ptr(ws), ws.numel() if ws is not None else 0, c.elem,
+                           _cabi.stream()), "pa_decay_scan")
+
+
+class DecayLinearAttention:
+    """Linear attention with a constant decay per head (cfg 'decay', one number per head): q, k, v = silu of their
+    projections, the matrix state per head and sequence in a float state slot, the heads' outputs normed together
+    (plain weight '<prefix>norm'), gated by sigmoid(W_g h), then the output product.  Reads q | k | v | g from a
+    projection buffer at a column offset."""
+
+    def __init__(self, model, prefix, cfg, W):
+        self.heads, self.dim, self.vdim = int(cfg["heads"]), int(cfg["dim"]), int(cfg["vdim"])
+        H = self.heads
+        if len(cfg["decay"]) != H:
+            raise ValueError(f"{prefix}: one decay per head expected")
+        shapes = (("q", H * self.dim), ("k", H * self.dim), ("v", H * self.vdim), ("g", H * self.vdim))
+        for name, rows in shapes:
+            if tuple(W[prefix + name].shape) != (rows, model.width):
+                raise ValueError(f"{prefix}{name}: shape does not match the config")
+        self.in_weight = torch.cat([W[prefix + n] for n, _ in shapes], 0)
+        self.in_bias = torch.zeros(self.in_weight.shape[0], dtype=self.in_weight.dtype)
+        self.in_cols = int(self.in_weight.shape[0])
+        self.decay = model._f32(torch.tensor([float(d) for d in cfg["decay"]], dtype=torch.float64))
+        self.norm = model._f32(W[prefix + "norm"])
+        self.w_o = model._weight(W[prefix + "o"])
+        self.alloc_state(model)
+
+    def alloc_state(self, model):
+        self.state = model.states.add_state(self.heads * self.dim * self.vdim)
+
+    def forward(self, c, proj, off):
+        H, d, vd = self.heads, self.dim, self.vdim
+        o = c.empty(c.R, H * vd, dtype=torch.float32)
+        decay_scan(c, self.state, o, H, H, d, vd, (proj, off), (proj, off + H * d), (proj, off + 2 * H * d), act=1,
+                   decay=self.decay)
+        on = c.empty(c.R, H * vd)
+        _chk(c.lib.pa_gated_rms_norm(o.data_ptr(), c.R, H * vd, 1, proj.data_ptr(), proj.stride(0), off + 2 * H * d + H * vd, 2,
+                                     self.norm.data_ptr(), c.model.eps, on.data_ptr(), c.elem, _cabi.stream()),
+             "pa_gated_rms_norm")
+        return c.model._linear(on, self.w_o)
+
+
+class SoftmaxAttentionMixer:
+    """A MaskedAttention as a layer's only mixer: one fused q | k | v product, attention, output product."""
+    kind = "attention"
+
+    def __init__(self, model, prefix, cfg, W, **constants):
+        self.core = MaskedAttention(model, prefix, cfg, W, **constants)
+        self.w_in, self.b_in = model._weight(self.core.in_weight), model._bias(self.core.in_bias)
+
+    def new_pass(self, model):
+        m = copy.copy(self)
+        m.core = copy.copy(self.core)
+        m.core.alloc_state(model)
+        return m
+
+    def forward(self, c, h):
+        proj = c.model._linear(h, self.w_in, bias=self.b_in)
+        return self.core.project_out(c, self.core.attend(c, proj, 0))
+
+
+class ParallelMixer:
+    """Two mixers side by side on the same input, left_scale * left + right_scale * right: a MaskedAttention (cfg 'left')
+    and a DecayLinearAttention (cfg 'right').  Everything that reads the input is ONE product."""
+    kind = "parallel"
+
+    def __init__(self, model, prefix, cfg, W, left=None, right=None):
+        self.left = MaskedAttention(model, prefix + "left.", cfg["left"], W, **(left or {}))
+        self.right = DecayLinearAttention(model, prefix + "right.", cfg["right"], W, **(right or {}))
+        self.left_scale, self.right_scale = float(cfg["left_scale"]), float(cfg["right_scale"])
+        self.w_in = model._weight(torch.cat([self.left.in_weight, self.right.in_weight], 0))
+        self.b_in = model._bias(torch.cat([self.left.in_bias, self.right.in_bias], 0))
+
+    def new_pass(self, model):
+        m = copy.copy(self)
+        m.left, m.right = copy.copy(self.left), copy.copy(self.right)
+        m.left.alloc_state(model)
+        m.right.alloc_state(model)
+        return m
+
+    def forward(self, c, h):
+        proj = c.model._linear(h, self.w_in, bias=self.b_in)
+        left = self.left.project_out(c, self.left.attend(c, proj, 0))
+        right = self.right.forward(c, proj, self.left.in_cols)
+        return dict(y=left, y_scale=self.left_scale, y2=right, y2_scale=self.right_scale)
+
+
+class Mamba2Mixer:
+    """Selective state space layer with scalar decay per head (state-space duality form): W_in h = [z | x | B | C | dt]
+    (inner = heads * vdim, B and C of `groups` x `state`), causal convolution + silu over [x | B | C] whose last taps - 1
+    inputs are carried per sequence, dt = softplus(dt + dt_bias), the matrix state per head in a float slot, y * silu(z),
+    RMS norm in norm_groups parts, output product."""
+    kind = "mamba2"
+
+    def __init__(self, model, prefix, cfg, W):
+        self.heads, self.vdim, self.state_dim = int(cfg["heads"]), int(cfg["vdim"]), int(cfg["state"])
+        self.groups, self.taps, self.norm_groups = int(cfg["groups"]), int(cfg["conv"]), int(cfg["norm_groups"])
+        H, P, N, G = self.heads, self.vdim, self.state_dim, self.groups
+        self.inner = H * P
+        self.channels = self.inner + 2 * G * N
+        if H % G or self.inner % self.norm_groups:
+            raise ValueError(f"{prefix}: heads must be a multiple of groups and heads * vdim of norm_groups")
+        if not 1 <= self.taps <= 8:
+            raise ValueError(f"{prefix}: 1 to 8 convolution taps are served")
+        want = {"in": (2 * self.inner + 2 * G * N + H, model.width), "conv": (self.channels, self.taps),
+                "conv.b": (self.channels,), "dt_bias": (H,), "A_log": (H,), "D": (H,), "norm": (self.inner,),
+                "o": (model.width, self.inner)}
+        for name, shape in want.items():
+            if tuple(W[prefix + name].shape) != shape:
+                raise ValueError(f"{prefix}{name}: shape {tuple(W[prefix + name].shape)} does not match the config {shape}")
+        self.w_in = model._weight(W[prefix + "in"])
+        self.conv_w, self.conv_b = model._f32(W[prefix + "conv"]), model._f32(W[prefix + "conv.b"])
+        self.dt_bias, self.a_log, self.skip = (model._f32(W[prefix + n]) for n in ("dt_bias", "A_log", "D"))
+        self.norm = model._f32(W[prefix + "norm"])
+        self.w_o = model._weight(W[prefix + "o"])
+        self.alloc_state(model)
+
+    def alloc_state(self, model):
+        self.state = model.states.add_state(self.heads * self.state_dim * self.vdim)
+        self.conv_state = model.states.add_state(max(1, (self.taps - 1) * self.channels))
+
+    def new_pass(self, model):
+        m = copy.copy(self)
+        m.alloc_state(model)
+        return m
+
+    def forward(self, c, h):
+        b, lib, s, R = c.batch, c.lib, _cabi.stream(), c.R
+        H, P, N, G, inner, C = self.heads, self.vdim, self.state_dim, self.groups, self.inner, self.channels
+        proj = c.model._linear(h, self.w_in)
+        chunks, nch, _s0, _sn = b.chunk_items(CONV_CHUNK)
+        xbc = c.empty(R, C)
+        _chk(lib.pa_causal_conv_silu(proj.data_ptr(), proj.stride(0), inner, C, self.taps, self.conv_w.data_ptr(),
+                                     self.conv_b.data_ptr(), self.conv_state.data_ptr(), chunks.data_ptr(), nch,
+                                     xbc.data_ptr(), C, c.elem, s), "pa_causal_conv_silu")
+        _chk(lib.pa_conv_state_update(proj.data_ptr(), proj.stride(0), inner, C, self.taps, b.seq_start.data_ptr(),
+                                      b.seq_len.data_ptr(), b.seq_slot.data_ptr(), b.num_seqs, self.conv_state.data_ptr(),
+                                      c.elem, s), "pa_conv_state_update")
+        y = c.empty(R, inner, dtype=torch.float32)
+        decay_scan(c, self.state, y, H, G, N, P, (xbc, inner + G * N), (xbc, inner), (xbc, 0), act=0,
+                   dt=(proj, 2 * inner + 2 * G * N), dt_bias=self.dt_bias, a_log=self.a_log, skip=self.skip)
+        yn = c.empty(R, inner)
+        _chk(lib.pa_gated_rms_norm(y.data_ptr(), R, inner, self.norm_groups, proj.data_ptr(), proj.stride(0), 0, 1,
+                                   self.norm.data_ptr(), c.model.eps, yn.data_ptr(), c.elem, s), "pa_gated_rms_norm")
+        return c.model._linear(yn, self.w_o)
+
+
 MIXERS = {"mingru": MinGRUMixer, "attention": DiffAttentionMixer, "latent_attention": LatentAttentionMixer}
 
 
@@ -350,12 +641,18 @@ class MoEFF:
     score ('sigmoid' / 'softmax' over all experts, the `top` largest scores, or 'softmax_chosen': the `top` largest
     logits, softmax over those only), an optional router bias ('<prefix>router.b'), weight_on ('input': the score scales
     the expert's input row; 'output': the weighted sum of the experts' outputs), gated experts W_down(act(W_gate a) *
-    W_up a) or plain ones W_down act(W_up a), and an optional gated shared expert."""
+    W_up a) or plain ones W_down act(W_up a), and an optional shared expert (gated per token where '<prefix>shared.sg'
+    exists).  cfg router.groups {count, keep}: experts in `count` equal groups of neighbours, only the `keep` groups with
+    the largest maxima can be chosen."""
     kind = "moe"
 
     def __init__(self, model, prefix, cfg, W, score="sigmoid", weight_on="input", act="silu", gated=True):
         self.experts, self.top = int(cfg["router"]["experts"]), int(cfg["router"]["top"])
         self.ff = int(cfg["expert"]["ff"])
+        grp = cfg["router"].get("groups") or {}
+        self.ngroups, self.keep = int(grp.get("count", 1)), int(grp.get("keep", grp.get("count", 1)))
+        if self.experts % self.ngroups or not 1 <= self.keep <= self.ngroups or self.keep * (self.experts // self.ngroups) < self.top:
+            raise ValueError("routed feed-forward: expert groups do not fit experts / top")
         self.score_fn, self.weight_on, self.act, self.gated = _SCORE_FN[score], weight_on, _EXPERT_ACT[act], bool(gated)
         if weight_on not in ("input", "output") or not 0 < self.top <= self.experts:
             raise ValueError("routed feed-forward: bad constants")
@@ -381,10 +678,10 @@ class MoEFF:
         sel_id, sel_w = c.empty(pairs, **i32), c.empty(pairs, **f32)
         sh = self.shared
         sgate = c.empty(R, **f32) if sh and sh["w_sg"] is not None else None
-        _chk(lib.pa_router_topk(h.data_ptr(), self.w_router.data_ptr(), _cabi.ptr(self.b_router),
-                                _cabi.ptr(sh["w_sg"]) if sgate is not None else None, R, wdt, self.experts, self.top,
-                                self.score_fn, 0, sel_id.data_ptr(), sel_w.data_ptr(), _cabi.ptr(sgate), c.elem, s),
-             "pa_router_topk")
+        _chk(lib.pa_router_topk_grouped(h.data_ptr(), self.w_router.data_ptr(), _cabi.ptr(self.b_router),
+                                        _cabi.ptr(sh["w_sg"]) if sgate is not None else None, R, wdt, self.experts,
+                                        self.top, self.score_fn, 0, self.ngroups, self.keep, sel_id.data_ptr(),
+                                        sel_w.data_ptr(), _cabi.ptr(sgate), c.elem, s), "pa_router_topk_grouped")
         order = c.empty(pairs, **i32)
         meta = c.empty(lib.pa_moe_meta_ints(pairs, self.experts), **i32)
         _chk(lib.pa_moe_sort(sel_id.data_ptr(), pairs, self.experts, order.data_ptr(), meta.data_ptr(), s), "pa_moe_sort")
@@ -414,6 +711,11 @@ DESIGNS = {
                                             "moe": dict(score="sigmoid", weight_on="input", act="silu", gated=True)}),
     "Domilix": dict(wiring="post_norm", ff={"dense": dict(act="relu", gated=True),
                                             "moe": dict(score="softmax_chosen", weight_on="output", act="relu2", gated=False)}),
+    "Dubarax": dict(wiring="pre_norm",
+                    mixers={"attention": (SoftmaxAttentionMixer, dict(mask="window", bias="bucket", softcap=True)),
+                            "parallel": (ParallelMixer, dict(left=dict(mask="chunk", bias="slope", slope_exp=8.0))),
+                            "mamba2": (Mamba2Mixer, {})},
+                    ff={"moe": dict(score="softmax", weight_on="output", act="silu", gated=True)}),
 }
 
 
@@ -444,9 +746,10 @@ class HybridDecoder:
             raise ValueError("embed does not match config vocab / width")
         self.embed = W["embed"].to(self.device, self.act_dtype).contiguous()
         self.head = self._weight(W["head"])
-        post = self.wiring == "post_norm"
-        self.final_gain = 1.0 if post else float(W["final.norm"].to(torch.float32))
-        self.final_gain_vec = self._f32(W["final.norm"].reshape(-1)) if post else None
+        post, pre = self.wiring == "post_norm", self.wiring == "pre_norm"
+        self.final_gain = 1.0 if post or pre else float(W["final.norm"].to(torch.float32))
+        self.final_gain_vec = self._f32(W["final.norm"].reshape(-1)) if post else self._gain1p(W["final.norm"]) if pre else None
+        mixers = self.design.get("mixers") or {k: (v, {}) for k, v in MIXERS.items()}
         self.layers = []
         for i, lc in enumerate(config["layers"]):
             L = _Layer()
@@ -455,20 +758,55 @@ class HybridDecoder:
                 L.gain1 = self._f32(W[p + "norm1"].reshape(-1))
                 L.gain2 = self._f32(W[p + "norm2"].reshape(-1)) if lc.get("mlp") else None
                 L.shift = L.prev = None
+            elif pre:   # per-channel gains of the norms in front of the two sublayers, stored around zero
+                L.gain1 = self._gain1p(W[p + "norm1"])
+                L.gain2 = self._gain1p(W[p + "norm2"]) if lc.get("mlp") else None
+                L.shift = L.prev = None
             else:
                 L.gain = float(W[p + "norm1"].to(torch.float32))
                 L.shift = self._f32(W[p + "shift"]) if p + "shift" in W else None
                 L.prev = self.states.add_state(self.width) if L.shift is not None else None
-            if lc["type"] not in MIXERS:
+            if lc["type"] not in mixers:
                 raise ValueError(f"unknown mixer type {lc['type']!r}")
-            L.mixer = MIXERS[lc["type"]](self, p + "mix.", lc.get("mixer") or {}, W)
+            mixer_cls, constants = mixers[lc["type"]]
+            L.mixer = mixer_cls(self, p + "mix.", lc.get("mixer") or {}, W, **constants)
             mc = lc.get("mlp")
             L.ff = None
             if mc:
                 if mc["kind"] not in FEED_FORWARDS:
                     raise ValueError(f"unknown feed-forward kind {mc['kind']!r}")
+                if mc["kind"] not in self.design["ff"]:
+                    raise ValueError(f"feed-forward kind {mc['kind']!r} is not part of this design")
                 L.ff = FEED_FORWARDS[mc["kind"]](self, p + "mlp.", mc, W, **self.design["ff"][mc["kind"]])
             self.layers.append(L)
+        self._build_runs(config.get("loop"), W)
+
+    def _build_runs(self, loop, W):
+        """The order in which layers RUN: (layer, mixer, pass number or None).  A looped block [start, stop) runs `times`
+        times in a row with the same weights; every pass after the first gets mixers with a cache / state of their own
+        (new_pass), and its first run carries the pass number: the block input x <- W_in [x | x0] + step[t] comes first."""
+        n = len(self.layers)
+        self.loop_in = self.loop_step = None
+        if not loop or int(loop.get("times", 0)) < 1 or int(loop["stop"]) <= int(loop["start"]):
+            self.runs = [(L, L.mixer, None) for L in self.layers]
+            return
+        if self.wiring != "pre_norm":
+            raise ValueError("looped blocks are served in the pre-norm wiring")
+        a, b, times = int(loop["start"]), int(loop["stop"]), int(loop["times"])
+        if not 0 <= a < b <= n:
+            raise ValueError("loop: start / stop outside the layer list")
+        if tuple(W["loop.in"].shape) != (self.width, 2 * self.width) or tuple(W["loop.step"].shape) != (times, self.width):
+            raise ValueError("loop.in / loop.step do not match width / times")
+        self.loop_in = self._weight(W["loop.in"])
+        self.loop_step = self._f32(W["loop.step"])
+        self.runs = [(L, L.mixer, None) for L in self.layers[:a]]
+        for t in range(times):
+            for i in range(a, b):
+                L = self.layers[i]
+                if t and not hasattr(L.mixer, "new_pass"):
+                    raise ValueError(f"mixer {L.mixer.kind!r} cannot run in a looped block")
+                self.runs.append((L, L.mixer if t == 0 else L.mixer.new_pass(self), t if i == a else None))
+        self.runs += [(L, L.mixer, None) for L in self.layers[b:]]
 
     @classmethod
     def from_pretrained(cls, path, dtype="bfloat16", **kw):
@@ -479,6 +817,14 @@ class HybridDecoder:
     # ---- weights ----------------------------------------------------------------------------------------------------
     def _f32(self, t):
         return t.to(torch.float32).to(self.device).contiguous()
+
+    def _gain1p(self, t):
+        """1 + w of a norm weight stored around zero (float)."""
+        return (1.0 + t.reshape(-1).to(torch.float32)).to(self.device).contiguous()
+
+    def _bias(self, t):
+        """A linear layer's bias for _linear: the activation type for the vendor GEMM's epilogue, float for the fp32 kernel."""
+        return t.to(self.act_dtype).to(self.device).contiguous()
 
     def _weight_raw(self, t):
         """[.., out, in] in the activation type (the grouped kernels read the stored orientation)."""
@@ -491,7 +837,7 @@ class HybridDecoder:
             return t.to(torch.float32).t().contiguous().to(self.device)
         return self._weight_raw(t)
 
-    def _linear(self, x, w, out_dtype=None):
+    def _linear(self, x, w, out_dtype=None, bias=None):
         R = x.shape[0]
         if self.act_dtype == torch.float32:
             K, N = w.shape
@@ -499,13 +845,15 @@ class HybridDecoder:
             need = self._lib.pa_linear_workspace_bytes(R, K, N)
             if need and (self._ws is None or self._ws.numel() < need):
                 self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
-            _chk(self._lib.pa_linear_f32_exact(x.data_ptr(), w.data_ptr(), None, R, K, N, 0, out.data_ptr(),
+            _chk(self._lib.pa_linear_f32_exact(x.data_ptr(), w.data_ptr(), _cabi.ptr(bias), R, K, N, 0, out.data_ptr(),
                                                _cabi.ptr(self._ws) if need else None, self._ws.numel() if need else 0,
                                                _cabi.stream()), "pa_linear_f32_exact")
             return out
         if out_dtype == torch.float32:
+            if bias is not None:
+                raise ValueError("_linear: no bias with a float result of bfloat16 operands")
             return torch.mm(x, w.t(), out_dtype=torch.float32)
-        return torch.nn.functional.linear(x, w)
+        return torch.nn.functional.linear(x, w, bias)
 
     # ---- the step ---------------------------------------------------------------------------------------------------
     def forward(self, batch, want_rows=None):
@@ -519,6 +867,8 @@ class HybridDecoder:
                                           self.embed_scale, x.data_ptr(), s), "pa_embedding_rows_scaled")
         if self.wiring == "post_norm":
             self._post_norm_layers(c, x)
+        elif self.wiring == "pre_norm":
+            x = self._pre_norm_layers(c, x)
         for L in self.layers if self.wiring == "parallel" else ():
             h = c.empty(R, W)
             hs = c.empty(R, W) if L.shift is not None else None
@@ -574,5 +924,47 @@ class HybridDecoder:
                 h = x if f32 else nxt
             if self.layer_hook is not None:
                 self.layer_hook(x)
+
+    def _pre_norm_layers(self, c, x):
+        """x += mixer(N1(x)), then x += ff(N2(x)), over self.runs.  The residual sum stays float; every add to x is fused
+        with the norm in front of the NEXT sublayer (pa_residual_add_prenorm), which leaves that sublayer's operand in the
+        activation type.  Returns the residual (a looped block's input product makes a new tensor)."""
+        lib, R, W, s = self._lib, c.R, self.width, _cabi.stream()
+        x0 = x.clone() if self.loop_in is not None else None
+
+        def add_norm(x, add, gain):
+            """x += the addends of `add`; returns N(x) * gain in the activation type (None without a gain)."""
+            if not add and gain is None:
+                return None
+            h = c.empty(R, W) if gain is not None else None
+            if add.get("shared_gate") is not None:
+                raise ValueError("a gated shared expert is not served in the pre-norm wiring")
+            y = add.get("y", add.get("dense"))
+            _chk(lib.pa_residual_add_prenorm(x.data_ptr(), R, W, _cabi.ptr(y), add.get("y_scale", 1.0), _cabi.ptr(add.get("y2")),
+                                             add.get("y2_scale", 1.0), _cabi.ptr(add.get("routed")), _cabi.ptr(add.get("sel_w")),
+                                             add.get("top", 0), _cabi.ptr(add.get("shared")), _cabi.ptr(add.get("bias")),
+                                             self.eps, _cabi.ptr(gain), _cabi.ptr(h), c.elem, s), "pa_residual_add_prenorm")
+            return h
+
+        pending = {}
+        for L, mixer, pass_t in self.runs:
+            if pass_t is not None:
+                add_norm(x, pending, None)
+                cat = c.empty(R, 2 * W)
+                _chk(lib.pa_concat_rows(x.data_ptr(), x0.data_ptr(), R, W, cat.data_ptr(), c.elem, s), "pa_concat_rows")
+                x = self._linear(cat, self.loop_in, out_dtype=torch.float32)
+                pending = dict(bias=self.loop_step[pass_t])
+            h = add_norm(x, pending, L.gain1)
+            mix = mixer.forward(c, h)
+            pending = mix if isinstance(mix, dict) else dict(y=mix)
+            if L.ff is not None:
+                h = add_norm(x, pending, L.gain2)
+                pending = L.ff.forward(c, h)
+            if self.layer_hook is not None:
+                add_norm(x, pending, None)
+                pending = {}
+                self.layer_hook(x)
+        add_norm(x, pending, None)
+        return x
 
     layer_hook = None   # debugging aid: called with the float residual after every layer

@@ -56,6 +56,26 @@ class RaggedBatch:
             self._cache[key] = out
         return self._cache[key]
 
+    def chunk_items(self, chunk):
+        """Every portion cut into runs of at most `chunk` consecutive tokens (0: whole portions), in portion order, as work
+        items of the convolution and matrix-state scan kernels: ([n, 4] int32 device tensor of (first row, tokens, slot,
+        offset of the first token within its portion), n, first item per portion, items per portion)."""
+        key = ("ci", chunk)
+        if key not in self._cache:
+            items, s0, sn = [], [], []
+            for r0, n, slot, _p0 in self.portions:
+                s0.append(len(items))
+                step = chunk if chunk > 0 else n
+                for o in range(0, n, step):
+                    items.append((r0 + o, min(step, n - o), slot, o))
+                sn.append(len(items) - s0[-1])
+            t = torch.tensor(items, dtype=torch.int32).reshape(-1, 4)
+            b = torch.tensor([s0, sn], dtype=torch.int32)
+            if self.device.type == "cuda":
+                t, b = t.pin_memory().to(self.device, non_blocking=True), b.pin_memory().to(self.device, non_blocking=True)
+            self._cache[key] = (t, len(items), b[0], b[1])
+        return self._cache[key]
+
     def scan_chunks(self, chunk):
         """Chunk lists of the chunked recurrent scan: (chunk_start, chunk_len, seq_chunk0, seq_nchunks) device int32
         tensors and the chunk count."""
