@@ -274,6 +274,10 @@ template <typename T, int DPT>
 static int ds_launch(const DecayScanParams& p, int nitems, int NS, cudaStream_t st) {
     const size_t smem = ((size_t)2 * kDsTokens * NS * DPT + 2 * kDsTokens + (NS > 1 ? (size_t)kDsTokens * NS * kDsCols : 0)) * sizeof(float);
     dim3 grid((unsigned)nitems, (unsigned)p.heads, (unsigned)((p.vdim + kDsCols - 1) / kDsCols));
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(decay_scan_kernel<T, DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
     decay_scan_kernel<T, DPT><<<grid, kDsCols * NS, smem, st>>>(p);
     PA_RETURN_LAUNCH_STATUS();
 }
