@@ -27,6 +27,8 @@ extra  = the other BASELINE.json configurations under the same clock (benchmarks
          equal size; the default workload and its JSON contract are untouched by it.
 --latent: likewise (benchmarks/latent.py): the same stack serving the `Domilix` design (latent attention, post-norm
          wiring) next to the `Megusun` design at equal size, and its kernels against their rooflines.
+--dubarax: likewise (benchmarks/dubarax.py): the stack serving the `Dubarax` design (pre-norm wiring, a looped block,
+         windowed / chunked attention, linear attention, a state-space mixer, group-limited experts) next to `Megusun`.
 N > 1: one process per GPU (torchrun), rows sharded across ranks, no data-path collective in the headline
          step; c5_splitkv is the mode with an exchange.
 """
@@ -67,6 +69,11 @@ def parse():
                     help="instead of the headline workload: prefill / decode throughput of the config-driven hybrid stack "
                          "(design Megusun) at realistic layer sizes next to CUDADecoder at equal size, and its kernels "
                          "against their rooflines (benchmarks/hybrid.py); one JSON line")
+    ap.add_argument("--dubarax", action="store_true",
+                    help="instead of the headline workload: prefill / decode throughput of the config-driven stack serving "
+                         "the Dubarax design (windowed / chunked attention, linear attention, state space, grouped router) at "
+                         "realistic layer sizes next to the Megusun design at equal size, and its kernels against their "
+                         "rooflines (benchmarks/dubarax.py); one JSON line")
     ap.add_argument("--latent", action="store_true",
                     help="instead of the headline workload: prefill / decode throughput of the config-driven stack serving "
                          "the Domilix design (latent attention) at realistic layer sizes next to the Megusun design at "
@@ -448,6 +455,10 @@ def main():
     if args.hybrid:
         from benchmarks import hybrid
         print(json.dumps({"bench": "hybrid", **hybrid.run()}, default=float))
+        return
+    if args.dubarax:
+        from benchmarks import dubarax
+        print(json.dumps({"bench": "dubarax", **dubarax.run()}, default=float))
         return
     if args.latent:
         from benchmarks import latent

@@ -228,6 +228,423 @@ static int ma_dispatch(const MaskAttnParams& p, int ntiles, cudaStream_t st) {
     }
 }
 
+
+// ---- single-token tiles (decode) ------------------------------------------------------------------------------------
+// One CTA = one token x one key/value head; its R >= heads-per-kv-head rows are the query heads of the group.  Nothing is
+// staged: each of the 8 warps takes every 8th run of 32 keys of the visible range, a lane reads ITS key's row with 16-byte
+// loads straight into the dot products of every row (queries broadcast from shared memory), the warp does the online
+// softmax, then lanes switch to value columns and read each key's value row coalesced.  The 8 warps' (m, l, acc) are
+// merged through shared memory.  Needs dim a multiple of the 16-byte vector and R <= 8 (else the tile kernel serves).
+template <typename T> struct MaVec { static constexpr int N = 16 / sizeof(T); };
+
+template <typename T>
+__device__ __forceinline__ void ma_load16(const T* __restrict__ p, float (&f)[MaVec<T>::N]) {
+    const uint4 v = ldg_stream_128(p);
+    if (sizeof(T) == 4) {
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+    } else {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+}
+
+template <typename T, int R, int NV>
+__global__ void __launch_bounds__(kMaWarps * 32) masked_attention_decode_kernel(const MaskAttnParams p) {
+    extern __shared__ float smem[];
+    constexpr int VN = MaVec<T>::N;
+    const int kd = p.dim;
+    float* Qs = smem;                                   // [R][kd]
+    float* Ps = Qs + R * kd;                            // [warps][R][2 + vdim]
+    const int pstride = 2 + p.vdim;
+    const int hpg = p.heads / p.num_kv_heads;
+    const int* tile = p.tiles + 4 * blockIdx.x;
+    const int row0 = tile[0], slot = tile[2], pos = tile[3];
+    const int g = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* kp = static_cast<const T*>(p.k_pool);
+    const T* vp = static_cast<const T*>(p.v_pool);
+    for (int idx = threadIdx.x; idx < R * kd; idx += blockDim.x) {
+        const int r = idx / kd, d = idx % kd;
+        Qs[idx] = r < hpg ? to_f32<T>(static_cast<const T*>(p.q)[(int64_t)row0 * p.q_stride + p.q_off + (int64_t)(g * hpg + r) * kd + d]) : 0.f;
+    }
+    __syncthreads();
+    float m[R], l[R], acc[R][NV], slope[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        m[r] = -INFINITY;
+        l[r] = 0.f;
+        slope[r] = p.bias_kind == 1 && r < hpg ? p.bias[g * hpg + r] : 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) acc[r][i] = 0.f;
+    }
+    const int first = ma_first_key(p, pos), total = pos + 1;
+    const int s_begin = first / kMaKeys, s_end = (total + kMaKeys - 1) / kMaKeys;
+    const int32_t* trow = p.table + ((int64_t)slot * p.num_kv_heads + g) * p.num_tiles;
+    for (int st = s_begin + warp; st < s_end; st += kMaWarps) {
+        const int j = st * kMaKeys + lane;
+        int prow = -1;                                  // pool row of this lane's key
+        if (j >= first && j < total && j / p.tile_size < p.num_tiles) {
+            const int page = trow[j / p.tile_size];
+            if (page >= 0 && page < p.total_pages) prow = page * p.tile_size + j % p.tile_size;
+        }
+        float s[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) s[r] = 0.f;
+        if (prow >= 0) {
+            const T* kr = kp + (int64_t)prow * kd;
+#pragma unroll 2
+            for (int d0 = 0; d0 < kd; d0 += VN) {
+                float kv[VN];
+                ma_load16<T>(kr + d0, kv);
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const float* q = Qs + r * kd + d0;
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) s[r] = fmaf(q[i], kv[i], s[r]);
+                }
+            }
+        }
+        const bool vis = prow >= 0;
+        float w[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float v = vis && r < hpg ? ma_score(p, s[r], pos, j, g * hpg + r, slope[r]) : -INFINITY;
+            const float n = fmaxf(m[r], warp_max(v));
+            const float c = n == -INFINITY ? 1.f : expf(m[r] - n);
+            w[r] = v == -INFINITY ? 0.f : expf(v - n);
+            l[r] = l[r] * c + warp_sum(w[r]);
+            m[r] = n;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) acc[r][i] *= c;
+        }
+        const int nk = min(kMaKeys, total - st * kMaKeys);
+#pragma unroll 4
+        for (int jj = 0; jj < nk; ++jj) {
+            const int pr = __shfl_sync(0xffffffffu, prow, jj);
+            float v[NV];
+#pragma unroll
+            for (int i = 0; i < NV; ++i) v[i] = 0.f;
+            if (pr >= 0) {
+                const T* vr = vp + (int64_t)pr * p.vdim;
+#pragma unroll
+                for (int i = 0; i < NV; ++i) v[i] = lane + 32 * i < p.vdim ? to_f32<T>(vr[lane + 32 * i]) : 0.f;
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float wj = __shfl_sync(0xffffffffu, w[r], jj);
+#pragma unroll
+                for (int i = 0; i < NV; ++i) acc[r][i] = fmaf(wj, v[i], acc[r][i]);
+            }
+        }
+    }
+    // ---- the warps' partials -> shared memory, merged by warp r for row r
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        float* dst = Ps + ((int64_t)warp * R + r) * pstride;
+        if (lane == 0) { dst[0] = m[r]; dst[1] = l[r]; }
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (lane + 32 * i < p.vdim) dst[2 + lane + 32 * i] = acc[r][i];
+    }
+    __syncthreads();
+    for (int r = warp; r < R; r += kMaWarps) {
+        if (r >= hpg) continue;
+        float M = -INFINITY;
+        for (int w = 0; w < kMaWarps; ++w) M = fmaxf(M, Ps[((int64_t)w * R + r) * pstride]);
+        float L = 0.f, b[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) b[i] = 0.f;
+        for (int w = 0; w < kMaWarps; ++w) {
+            const float* pw = Ps + ((int64_t)w * R + r) * pstride;
+            const float f = pw[0] == -INFINITY ? 0.f : expf(pw[0] - M);
+            L = fmaf(f, pw[1], L);
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+                if (lane + 32 * i < p.vdim) b[i] = fmaf(f, pw[2 + lane + 32 * i], b[i]);
+        }
+        T* dst = static_cast<T*>(p.out) + (int64_t)row0 * p.heads * p.vdim + (int64_t)(g * hpg + r) * p.vdim;
+        const float inv = 1.0f / L;
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (lane + 32 * i < p.vdim) dst[lane + 32 * i] = from_f32<T>(b[i] * inv);
+    }
+}
+
+template <typename T, int R, int NV>
+static int ma_decode_launch(const MaskAttnParams& p, int ntiles, cudaStream_t st) {
+    const size_t smem = ((size_t)R * p.dim + (size_t)kMaWarps * R * (2 + p.vdim)) * sizeof(float);
+    if (smem > 200 * 1024) return PA_ERR_UNSUPPORTED;
+    auto kern = masked_attention_decode_kernel<T, R, NV>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((unsigned)ntiles, (unsigned)p.num_kv_heads);
+    kern<<<grid, kMaWarps * 32, smem, st>>>(p);
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+// PA_ERR_UNSUPPORTED: this shape stays on the tile kernel
+template <typename T>
+static int ma_decode_dispatch(const MaskAttnParams& p, int ntiles, cudaStream_t st) {
+    const int hpg = p.heads / p.num_kv_heads, nv = (p.vdim + 31) / 32;
+    if (p.dim % MaVec<T>::N || hpg > 8 || nv > 8) return PA_ERR_UNSUPPORTED;
+    if ((uintptr_t)p.k_pool % 16) return PA_ERR_UNSUPPORTED;
+    const int NVc = nv <= 1 ? 1 : nv <= 2 ? 2 : nv <= 4 ? 4 : 8;
+#define PA_MA_DEC(RR)                                                   \
+    switch (NVc) {                                                      \
+        case 1: return ma_decode_launch<T, RR, 1>(p, ntiles, st);       \
+        case 2: return ma_decode_launch<T, RR, 2>(p, ntiles, st);       \
+        case 4: return ma_decode_launch<T, RR, 4>(p, ntiles, st);       \
+        default: if (RR <= 4) return ma_decode_launch<T, (RR <= 4 ? RR : 4), 8>(p, ntiles, st); return PA_ERR_UNSUPPORTED; \
+    }
+    if (hpg <= 2) { PA_MA_DEC(2) }
+    if (hpg <= 4) { PA_MA_DEC(4) }
+    PA_MA_DEC(8)
+#undef PA_MA_DEC
+}
+
+// ---- prompt portions on the tensor cores (bfloat16) -------------------------------------------------------------------
+// One CTA = up to 64 consecutive tokens of one portion x ONE query head; 4 warps, warp w owns rows 16 w .. 16 w + 15:
+// a flash-attention (mma.sync m16n8k16, bfloat16 operands, float accumulators) over staged key and value tiles of 64 keys,
+// located through the page table and brought in with 16-byte cp.async copies into two buffers (the copies of step t + 1
+// fly while step t is multiplied).  Only the key steps between the first key the tile's first token sees and its last
+// token are visited; a warp skips steps none of its rows can see.  The dot products are raw q . k; scale, soft cap and
+// distance bias are applied to the float score.  Scores, the running maximum, the exponentials and their sum are float;
+// the weights enter the second product rounded to bfloat16, like every other matrix operand of this precision.
+// DIM and VDIM are the PADDED sizes (32, 64 or 128): the real dim / vdim values (any multiple of 8) sit at the start of
+// the columns and the rest is zero; 16-wide steps that are all padding are skipped.  A bias table of up to kMmBiasMax
+// distances is staged (this head's column) in shared memory.
+constexpr int kMmRows = 64, kMmKeys = 64, kMmThreads = 128, kMmPad = 8, kMmStages = 2, kMmBiasMax = 4096;
+
+__device__ __forceinline__ float ma_tanh(float x) {        // 1 - 2 / (e^{2x} + 1), relative error ~1e-6
+    const float e = __expf(2.0f * x);
+    return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
+
+template <int DIM, int VDIM>
+__global__ void __launch_bounds__(kMmThreads) masked_attention_mma_kernel(const MaskAttnParams p) {
+    constexpr int KS = DIM + kMmPad, VS = VDIM + kMmPad, NT = VDIM / 8, NST = kMmStages;
+    extern __shared__ __align__(16) unsigned char mm_smem[];
+    bf16_t* Qs = reinterpret_cast<bf16_t*>(mm_smem);         // [64][KS]
+    bf16_t* Ks = Qs + kMmRows * KS;                           // [NST][64][KS]
+    bf16_t* Vs = Ks + NST * kMmKeys * KS;                     // [NST][64][VS]
+    float* Bs = reinterpret_cast<float*>(Vs + NST * kMmKeys * VS);   // [bias_len] (bias_kind 2, bias_len <= kMmBiasMax)
+    __shared__ int key_ok[NST][kMmKeys];
+
+    const int* tile = p.tiles + 4 * blockIdx.x;
+    const int row0 = tile[0], ntok = tile[1], slot = tile[2], pos0 = tile[3];
+    const int head = blockIdx.y, hpg = p.heads / p.num_kv_heads, g = head / hpg;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int rbase = warp * 16;
+    const bool active = rbase < ntok;
+    const bf16_t* kp = static_cast<const bf16_t*>(p.k_pool);
+    const bf16_t* vp = static_cast<const bf16_t*>(p.v_pool);
+    const int32_t* trow = p.table + ((int64_t)slot * p.num_kv_heads + g) * p.num_tiles;
+    const int total = pos0 + ntok;
+    const int kt0 = ma_first_key(p, pos0) / kMmKeys, nkt = (total + kMmKeys - 1) / kMmKeys;
+    const int dim = p.dim, vdim = p.vdim;
+    const bool bias_smem = p.bias_kind == 2 && p.bias_len <= kMmBiasMax;
+
+    for (int c = tid; c < kMmRows * (DIM / 8); c += kMmThreads) {
+        const int r = c / (DIM / 8), cv = (c % (DIM / 8)) * 8;
+        const bool ok = r < ntok && cv < dim;
+        const bf16_t* src = static_cast<const bf16_t*>(p.q) + (ok ? (int64_t)(row0 + r) * p.q_stride + p.q_off + (int64_t)head * dim + cv : 0);
+        cp_async_16(smem_u32(Qs + r * KS + cv), src, ok);
+    }
+    if (bias_smem)
+        for (int d = tid; d < p.bias_len; d += kMmThreads) Bs[d] = p.bias[(int64_t)d * p.heads + head];
+    auto pool_row = [&](int j) -> int64_t {
+        if (j < total && j / p.tile_size < p.num_tiles) {
+            const int page = trow[j / p.tile_size];
+            if (page >= 0 && page < p.total_pages) return (int64_t)page * p.tile_size + j % p.tile_size;
+        }
+        return -1;
+    };
+    // two threads per key: ONE page look-up per thread and step; a thread copies every second 16-byte piece of its key's
+    // row and of its value row
+    auto load_tile = [&](int kt, int buf) {
+        const int key = tid >> 1, q2 = tid & 1;
+        const int64_t pr = pool_row(kt * kMmKeys + key);
+        if (q2 == 0) key_ok[buf][key] = pr >= 0;
+        bf16_t* kdst = Ks + (buf * kMmKeys + key) * KS;
+        const bf16_t* ksrc = kp + (pr >= 0 ? pr * dim : 0);
+#pragma unroll
+        for (int i = 0; i < DIM / 16; ++i) {
+            const int cv = (q2 + 2 * i) * 8;
+            const bool ok = pr >= 0 && cv < dim;
+            cp_async_16(smem_u32(kdst + cv), ok ? ksrc + cv : kp, ok);
+        }
+        bf16_t* vdst = Vs + (buf * kMmKeys + key) * VS;
+        const bf16_t* vsrc = vp + (pr >= 0 ? pr * vdim : 0);
+#pragma unroll
+        for (int i = 0; i < VDIM / 16; ++i) {
+            const int cv = (q2 + 2 * i) * 8;
+            const bool ok = pr >= 0 && cv < vdim;
+            cp_async_16(smem_u32(vdst + cv), ok ? vsrc + cv : vp, ok);
+        }
+    };
+#pragma unroll
+    for (int t = 0; t < NST - 1; ++t) {
+        if (kt0 + t < nkt) load_tile(kt0 + t, t);
+        cp_async_commit();
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[t][c] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    int rpos[2], rlo[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        rpos[i] = pos0 + rbase + (lane >> 2) + 8 * i;
+        rlo[i] = ma_first_key(p, rpos[i]);
+    }
+    // the warp's rows together see keys [wlo, whi]
+    const int wlo = ma_first_key(p, pos0 + rbase), whi = pos0 + min(rbase + 15, ntok - 1);
+    const float slope = p.bias_kind == 1 ? p.bias[head] : 0.f;
+    const float inv_cap = p.softcap > 0.f ? 1.0f / p.softcap : 0.f;
+    constexpr float kLog2e = 1.4426950408889634f;
+
+    for (int kt = kt0; kt < nkt; ++kt) {
+        const int buf = (kt - kt0) % NST, c0 = kt * kMmKeys;
+        if (kt + NST - 1 < nkt) load_tile(kt + NST - 1, (kt - kt0 + NST - 1) % NST);
+        cp_async_commit();
+        cp_async_wait<NST - 1>();
+        __syncthreads();
+        if (active && c0 + kMmKeys - 1 >= wlo && c0 <= whi) {
+        float s[8][4];
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[t][c] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < DIM; ks += 16) {
+            if (ks >= dim) continue;                         // all padding
+            uint32_t a[4];
+            ldsm_x4(smem_u32(Qs + (rbase + (lane & 15)) * KS + ks + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(smem_u32(Ks + (buf * kMmKeys + np * 16 + (lane & 7) + ((lane >> 4) << 3)) * KS + ks + ((lane >> 3) & 1) * 8),
+                        b0, b1, b2, b3);
+                mma_bf16_16816(s[2 * np], a, b0, b1);
+                mma_bf16_16816(s[2 * np + 1], a, b2, b3);
+            }
+        }
+        // ---- float scores -> weights (log2 domain)
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+            const int col = t * 8 + 2 * (lane & 3);
+            const int2 okk = *reinterpret_cast<const int2*>(&key_ok[buf][col]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int i = c >> 1, j = c0 + col + (c & 1);
+                const bool vis = ((c & 1) ? okk.y : okk.x) && j <= rpos[i] && j >= rlo[i];
+                float v = s[t][c] * p.scale;
+                if (p.softcap > 0.f) v = p.softcap * ma_tanh(v * inv_cap);
+                if (p.bias_kind == 1) v -= slope * (float)(rpos[i] - j);
+                else if (p.bias_kind == 2 && vis) {
+                    const int dist = min(rpos[i] - j, p.bias_len - 1);
+                    v += bias_smem ? Bs[dist] : p.bias[(int64_t)dist * p.heads + head];
+                }
+                s[t][c] = vis ? v * kLog2e : -INFINITY;
+                mx[i] = fmaxf(mx[i], s[t][c]);
+            }
+        }
+        float ref[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float mn = fmaxf(m[i], mx[i]);
+            ref[i] = mn == -INFINITY ? 0.f : mn;
+            const float corr = exp2f(m[i] - ref[i]);         // m = -inf: 0 (nothing accumulated yet)
+            m[i] = mn;
+            l[i] *= corr;
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                o[t][2 * i] *= corr;
+                o[t][2 * i + 1] *= corr;
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                s[t][c] = exp2f(s[t][c] - ref[c >> 1]);
+                l[c >> 1] += s[t][c];
+            }
+        // ---- weighted sums
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            uint32_t a[4];
+            a[0] = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]);
+            a[1] = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
+            a[2] = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            a[3] = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int np = 0; np < NT / 2; ++np) {
+                if (np * 16 >= vdim) continue;               // all padding
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_trans(smem_u32(Vs + (buf * kMmKeys + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + np * 16 + (lane >> 4) * 8),
+                              b0, b1, b2, b3);
+                mma_bf16_16816(o[2 * np], a, b0, b1);
+                mma_bf16_16816(o[2 * np + 1], a, b2, b3);
+            }
+        }
+        }
+        __syncthreads();                                     // this buffer is free for the copies of step kt + NST
+    }
+    cp_async_wait<0>();
+    if (!active) return;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+        const int r = rbase + (lane >> 2) + 8 * i;
+        if (r >= ntok) continue;
+        const float inv = 1.0f / l[i];
+        bf16_t* dst = static_cast<bf16_t*>(p.out) + (int64_t)(row0 + r) * p.heads * vdim + (int64_t)head * vdim + 2 * (lane & 3);
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+            if (t * 8 < vdim) *reinterpret_cast<uint32_t*>(dst + t * 8) = pack_bf16x2(o[t][2 * i] * inv, o[t][2 * i + 1] * inv);
+    }
+}
+
+template <int DIM, int VDIM>
+static int mm_launch(const MaskAttnParams& p, int ntiles, cudaStream_t st) {
+    size_t smem = ((size_t)(kMmRows + kMmStages * kMmKeys) * (DIM + kMmPad) + (size_t)kMmStages * kMmKeys * (VDIM + kMmPad)) * sizeof(bf16_t);
+    if (p.bias_kind == 2 && p.bias_len <= kMmBiasMax) smem += (size_t)p.bias_len * sizeof(float);
+    auto kern = masked_attention_mma_kernel<DIM, VDIM>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((unsigned)ntiles, (unsigned)p.heads);
+    kern<<<grid, kMmThreads, smem, st>>>(p);
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+static bool mm_shape_ok(int dim, int vdim) { return dim % 8 == 0 && dim <= 128 && vdim % 8 == 0 && vdim <= 128; }
+static int mm_padded(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : 128; }
+
+// PA_ERR_UNSUPPORTED: this shape or these pointers stay on the float kernel
+static int mm_dispatch(const MaskAttnParams& p, int ntiles, cudaStream_t st) {
+    if (!mm_shape_ok(p.dim, p.vdim) || p.q_stride % 8 || p.q_off % 8) return PA_ERR_UNSUPPORTED;
+    if ((uintptr_t)p.q % 16 || (uintptr_t)p.k_pool % 16 || (uintptr_t)p.v_pool % 16 || (uintptr_t)p.out % 4) return PA_ERR_UNSUPPORTED;
+    const int dp = mm_padded(p.dim), vp = mm_padded(p.vdim);
+#define PA_MM_CASE(D, V) if (dp == D && vp == V) return mm_launch<D, V>(p, ntiles, st)
+    PA_MM_CASE(32, 32); PA_MM_CASE(32, 64); PA_MM_CASE(32, 128);
+    PA_MM_CASE(64, 32); PA_MM_CASE(64, 64); PA_MM_CASE(64, 128);
+    PA_MM_CASE(128, 32); PA_MM_CASE(128, 64); PA_MM_CASE(128, 128);
+#undef PA_MM_CASE
+    return PA_ERR_UNSUPPORTED;
+}
+
 }  // namespace pa
 
 using namespace pa;
@@ -257,12 +674,19 @@ PA_API int pa_masked_attention(const void* d_q, int64_t q_stride, int q_off, con
     p.softcap = softcap; p.mask_kind = mask_kind; p.mask_size = mask_size; p.bias_kind = bias_kind; p.bias = d_bias;
     p.bias_len = bias_len; p.out = d_out; p.head_rows = 0;
     if (elem != 4 && elem != 2) return PA_ERR_UNSUPPORTED;
-    (void)tile_kind;
+    if (tile_kind == 2) {       // on the tensor cores: tiles of up to pa_masked_attention_mma_tile_tokens tokens
+        if (elem != 2) return PA_ERR_UNSUPPORTED;
+        return mm_dispatch(p, num_q_tiles, as_stream(stream));
+    }
+    if (tile_kind == 1) {       // every tile is one token: the streaming kernel, where it serves the shape
+        const int st = elem == 4 ? ma_decode_dispatch<float>(p, num_q_tiles, as_stream(stream))
+                                 : ma_decode_dispatch<bf16_t>(p, num_q_tiles, as_stream(stream));
+        if (st != PA_ERR_UNSUPPORTED) return st;
+    }
     if (elem == 4) return ma_dispatch<float>(p, num_q_tiles, as_stream(stream));
     return ma_dispatch<bf16_t>(p, num_q_tiles, as_stream(stream));
 }
 
 PA_API int pa_masked_attention_mma_tile_tokens(int dim, int vdim, int elem) {
-    (void)dim; (void)vdim; (void)elem;
-    return 0;
+    return elem == 2 && mm_shape_ok(dim, vdim) ? kMmRows : 0;
 }

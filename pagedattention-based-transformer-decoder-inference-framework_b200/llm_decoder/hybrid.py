@@ -475,7 +475,7 @@ class DecayLinearAttention:
             if tuple(W[prefix + name].shape) != (rows, model.width):
                 raise ValueError(f"{prefix}{name}: shape does not match the config")
         self.in_weight = torch.cat([W[prefix + n] for n, _ in shapes], 0)
-        self.in_bias = torch.zeros(self.in_weight.shape[0], dtype=self.in_weight.dtype)
+        self.in_bias = torch.zeros(self.in_weight.shape[0], dtype=self.in_weight.dtype, device=self.in_weight.device)
         self.in_cols = int(self.in_weight.shape[0])
         self.decay = model._f32(torch.tensor([float(d) for d in cfg["decay"]], dtype=torch.float64))
         self.norm = model._f32(W[prefix + "norm"])

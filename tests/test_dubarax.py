@@ -624,6 +624,101 @@ def test_causal_convolution_kernel_alone(taps):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 16, 24), (6, 1, 96, 96), (8, 2, 64, 128), (3, 3, 40, 8), (2, 1, 128, 64)])
+@pytest.mark.parametrize("mask,size,bias", [("window", 37, "bucket"), ("window", 200, "bucket"), ("chunk", 50, "slope"), ("chunk", 64, None),
+                                            ("causal", 0, "bucket"), ("window", 5, "slope")])
+def test_attention_kernels_alone(heads, kv_heads, dim, vdim, mask, size, bias):
+    """The float tile kernel, the streaming single-token kernel and the tensor-core kernel over the same paged pool
+    (pages handed out in a scattered order) against softmax attention written out in float64: a 150-token portion that
+    starts at position 70 of its sequence, and single tokens at positions 0, 63, 64 and 219 of three others."""
+    from llm_decoder import _cabi
+    from llm_decoder.hybrid import MASK_KIND, log_distance_bucket
+    from llm_decoder.seq_state import SequenceStateCache
+    lib, dev = _cabi.lib(), torch.device("cuda")
+    g = torch.Generator().manual_seed(heads * 7 + dim)
+    per = heads // kv_heads
+    scale, cap = dim ** -0.5 * 2.0, 6.0 if bias == "bucket" else 0.0
+    ctx = [70, 0, 63, 219]                                  # tokens already cached per sequence
+    new = [150, 1, 2, 1]                                    # tokens of this step (the third: two single-token steps' worth)
+    for dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 2e-2)):
+        states = SequenceStateCache(4, 1024, 16, dev)
+        kv = states.add_kv_layer(kv_heads, dim, vdim, "f32" if dtype == torch.float32 else "bf16")
+        slots = [states.alloc() for _ in range(4)]
+        order = [2, 0, 3, 1]
+        for rnd_ in range(14):                              # interleave the sequences' growth so that their pages interleave
+            for i in order:
+                n = min(16, ctx[i] - rnd_ * 16)
+                if n > 0:
+                    states.extend(slots[i], n)
+        K = [torch.randn(ctx[i] + new[i], kv_heads * dim, generator=g).to(dtype) for i in range(4)]
+        V = [torch.randn(ctx[i] + new[i], kv_heads * vdim, generator=g).to(dtype) for i in range(4)]
+        Q = [torch.randn(new[i], heads * dim, generator=g).to(dtype) for i in range(4)]
+        # the cached part goes in through the same append call, as earlier steps would have left it
+        pt = kv.page_table_
+        for i in range(4):
+            if ctx[i]:
+                rows = torch.cat([K[i][:ctx[i]], V[i][:ctx[i]]], 1).to(dev)
+                kv.append_rows(rows, 0, kv_heads * dim, torch.full((ctx[i],), slots[i], dtype=torch.int32, device=dev),
+                               torch.arange(ctx[i], dtype=torch.int32, device=dev))
+        batch = states.make_batch([(slots[i], [0] * new[i]) for i in range(4)])
+        proj = torch.cat([torch.cat([Q[i], K[i][ctx[i]:], V[i][ctx[i]:]], 1) for i in range(4)], 0).to(dev)
+        kv.append_rows(proj, heads * dim, heads * dim + kv_heads * dim, batch.row_slot, batch.row_pos)
+        if bias == "bucket":
+            rel = torch.randn(9, heads, generator=g)
+            far = 120.0
+            n = int(far) + 1 if mask != "window" else min(int(far) + 1, size)
+            table = rel[torch.tensor([log_distance_bucket(d, 9, far) for d in range(n)])].contiguous()
+            bias_kind, bias_t = 2, table.to(dev)
+        elif bias == "slope":
+            slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)])
+            bias_kind, bias_t = 1, slopes.to(dev)
+        else:
+            bias_kind, bias_t = 0, None
+        want = []
+        for i in range(4):
+            q, k, v = Q[i].double(), K[i].double(), V[i].double()
+            out = torch.zeros(new[i], heads * vdim, dtype=torch.float64)
+            pos = torch.arange(ctx[i], ctx[i] + new[i])[:, None]
+            j = torch.arange(ctx[i] + new[i])[None, :]
+            dist = pos - j
+            vis = dist >= 0
+            if mask == "window":
+                vis &= dist < size
+            elif mask == "chunk":
+                vis &= (pos // size) == (j // size)
+            for h in range(heads):
+                gi = h // per
+                sc = q[:, h * dim:(h + 1) * dim] @ k[:, gi * dim:(gi + 1) * dim].T * scale
+                if cap:
+                    sc = cap * torch.tanh(sc / cap)
+                if bias == "bucket":
+                    sc = sc + table.double()[dist.clamp(0, table.shape[0] - 1), h]
+                elif bias == "slope":
+                    sc = sc - float(slopes[h]) * dist
+                out[:, h * vdim:(h + 1) * vdim] = torch.softmax(sc.masked_fill(~vis, -float("inf")), -1) @ v[:, gi * vdim:(gi + 1) * vdim]
+            want.append(out)
+        want = torch.cat(want, 0)
+        tt = lib.pa_masked_attention_tile_tokens(heads, kv_heads)
+        mt = lib.pa_masked_attention_mma_tile_tokens(dim, vdim, proj.element_size())
+        table_dev = pt.device_data()
+        for use_mma, use_stream in ((0, 0), (mt, 1)):
+            out = torch.zeros(sum(new), heads * vdim, dtype=dtype, device=dev)
+            for kind, group in batch.query_tiles(tt, use_mma, 16).items():
+                if group is None:
+                    continue
+                tiles, ntiles, _longest = group
+                rc = lib.pa_masked_attention(proj.data_ptr(), proj.stride(0), 0, kv.key_buffer_.data_ptr(), kv.value_buffer_.data_ptr(),
+                                             table_dev.data_ptr(), pt.num_beams_, pt.num_heads_, pt.num_tiles_, kv.total_pages_,
+                                             kv.tile_size_, tiles.data_ptr(), ntiles, heads, dim, vdim, scale, cap, MASK_KIND[mask],
+                                             size, bias_kind, _cabi.ptr(bias_t), int(bias_t.shape[0]) if bias_kind == 2 else 0,
+                                             out.data_ptr(), proj.element_size(), kind if (use_stream or kind != 1) else 0,
+                                             _cabi.stream())
+                assert rc == 0, (kind, rc)
+            err = (out.double().cpu() - want).abs().max().item()
+            assert err < tol * max(1.0, want.abs().max().item()), (dtype, use_mma, err)
+
+
+@pytest.mark.gpu
 def test_router_groups_kernel_alone():
     from llm_decoder import _cabi
     lib, dev = _cabi.lib(), torch.device("cuda")
