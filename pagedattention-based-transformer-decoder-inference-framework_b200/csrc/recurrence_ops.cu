@@ -99,122 +99,188 @@ struct DecayScanParams {
     // mode 1: fold a chunk from a zero state into part[item]; mode 2: replay a chunk from part[item] (no state written)
     const int32_t* items;
     int mode;
+    int vec;                                          // every staged piece of q, k and v starts on a 16-byte boundary
     float* part;                                      // [items][heads][dim * vdim + 1]: state, then the chunk's total decay
 };
 
 constexpr int kDsTokens = 16;                         // tokens staged per step
-constexpr int kDsCols = 64;                           // value columns per CTA
+constexpr int kDsCpt = 4;                             // value columns per thread
+constexpr int kDsMaxThreads = 128;
 
 __device__ __forceinline__ float softplus_f32(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-// CTA = kDsCols value columns x NS slices of the state's rows: thread (column, slice) keeps DPT rows of its column in
-// registers.  q, k, the decays and the input scales of kDsTokens tokens are staged in shared memory per step; a thread
-// reads its own v.  With NS > 1 the slices' partial outputs are summed through shared memory once per step.
-template <typename T, int DPT>
-__global__ void __launch_bounds__(256) decay_scan_kernel(const DecayScanParams p) {
+template <typename T>
+__device__ __forceinline__ void ds_load16(const T* __restrict__ p, float (&f)[16 / sizeof(T)]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    if (sizeof(T) == 4) {
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+    } else {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+}
+
+// A thread keeps a DPT x kDsCpt block of the state in registers: lane = (column group) * NSL + (row slice), so the NSL
+// threads that share a column group cover NSL * DPT >= dim rows and their partial outputs meet in a shuffle reduction.
+// q, k, v, the decays and the input scales of kDsTokens tokens are staged in shared memory per step (one 16-byte read of
+// q and of k feeds 4 x kDsCpt updates and as many output terms).  MODE 0: a portion from / to its state slot; 1: fold a
+// chunk from a zero state into part[item] (no outputs); 2: replay a chunk from part[item] (no state written).
+template <typename T, int DPT, int MODE>
+__global__ void __launch_bounds__(kDsMaxThreads) decay_scan_kernel(const DecayScanParams p, int NSL) {
     extern __shared__ __align__(16) float ds_smem[];
-    const int NS = blockDim.x / kDsCols;
-    const int dpad = NS * DPT;
+    const int dpad = NSL * DPT;
+    const int ccols = blockDim.x / NSL * kDsCpt;       // value columns of this CTA
     float* Qs = ds_smem;                               // [kDsTokens][dpad]
     float* Ks = Qs + kDsTokens * dpad;                 // [kDsTokens][dpad]
-    float* As = Ks + kDsTokens * dpad;                 // [kDsTokens] decay
+    float* Vs = Ks + kDsTokens * dpad;                 // [kDsTokens][ccols]
+    float* As = Vs + kDsTokens * ccols;                // [kDsTokens] decay
     float* Ss = As + kDsTokens;                        // [kDsTokens] input scale
-    float* Ps = Ss + kDsTokens;                        // [kDsTokens][NS][kDsCols] partial outputs (NS > 1)
-    const int col = threadIdx.x % kDsCols, slice = threadIdx.x / kDsCols;
-    const int h = blockIdx.y, c = blockIdx.z * kDsCols + col;
+    const int slice = threadIdx.x % NSL, cgrp = threadIdx.x / NSL;
+    const int h = blockIdx.y, cl = cgrp * kDsCpt, c = blockIdx.z * ccols + cl;
     const int g = h / (p.heads / p.groups);
     const int* it = p.items + 4 * blockIdx.x;
     const int row0 = it[0], n = it[1], slot = it[2];
-    const bool live = c < p.vdim;
     const int d0 = slice * DPT;
     const int64_t sz = (int64_t)p.dim * p.vdim;
 
-    float S[DPT];
-    const float* src = p.mode == 0 ? p.state + ((int64_t)slot * p.heads + h) * sz
-                     : p.mode == 2 ? p.part + ((int64_t)blockIdx.x * p.heads + h) * (sz + 1) : nullptr;
+    float S[DPT][kDsCpt];
+    const float* src = MODE == 0 ? p.state + ((int64_t)slot * p.heads + h) * sz
+                     : MODE == 2 ? p.part + ((int64_t)blockIdx.x * p.heads + h) * (sz + 1) : nullptr;
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) S[i] = (src && live && d0 + i < p.dim) ? src[(int64_t)(d0 + i) * p.vdim + c] : 0.f;
-    float total = 1.f;                                 // product of the decays (mode 1)
+    for (int i = 0; i < DPT; ++i)
+#pragma unroll
+        for (int j = 0; j < kDsCpt; ++j)
+            S[i][j] = (MODE != 1 && d0 + i < p.dim && c + j < p.vdim) ? src[(int64_t)(d0 + i) * p.vdim + c + j] : 0.f;
+    float total = 1.f;                                 // product of the decays (MODE 1)
     const float hd = p.dt ? 0.f : p.decay[h];
     const float a_rate = p.dt ? -expf(p.a_log[h]) : 0.f, dtb = p.dt ? p.dt_bias[h] : 0.f;
     const float skip = p.skip ? p.skip[h] : 0.f;
     const T* qb = static_cast<const T*>(p.q) + p.q_off + (int64_t)g * p.dim;
     const T* kb = static_cast<const T*>(p.k) + p.k_off + (int64_t)g * p.dim;
-    const T* vb = static_cast<const T*>(p.v) + p.v_off + (int64_t)h * p.vdim;
+    const T* vb = static_cast<const T*>(p.v) + p.v_off + (int64_t)h * p.vdim + (int64_t)blockIdx.z * ccols;
+    const int vcols = min(ccols, p.vdim - blockIdx.z * ccols);
 
+    // rows whose pieces start on 16-byte boundaries are staged with 16-byte loads (`vec`, checked by the host); the columns
+    // past dim / past this CTA's share of vdim are zeroed once and never written again
+    constexpr int VN = 16 / sizeof(T);
+    if (p.vec) {
+        for (int idx = threadIdx.x; idx < kDsTokens * dpad; idx += blockDim.x) Qs[idx] = Ks[idx] = 0.f;
+        for (int idx = threadIdx.x; idx < kDsTokens * ccols; idx += blockDim.x) Vs[idx] = 0.f;
+    }
     for (int t0 = 0; t0 < n; t0 += kDsTokens) {
         const int nt = min(kDsTokens, n - t0);
         __syncthreads();
+        if (p.vec) {
+            const int kvecs = p.dim / VN, vvecs = vcols / VN;
+            for (int idx = threadIdx.x; idx < nt * kvecs; idx += blockDim.x) {
+                const int t = idx / kvecs, d = (idx % kvecs) * VN;
+                float kf[VN], qf[VN];
+                ds_load16<T>(kb + (int64_t)(row0 + t0 + t) * p.k_stride + d, kf);
+                if (MODE != 1) ds_load16<T>(qb + (int64_t)(row0 + t0 + t) * p.q_stride + d, qf);
+#pragma unroll
+                for (int i = 0; i < VN; ++i) {
+                    if (MODE == 1) qf[i] = 0.f;
+                    if (p.act) { qf[i] = silu_f32(qf[i]); kf[i] = silu_f32(kf[i]); }
+                }
+#pragma unroll
+                for (int i = 0; i < VN; i += 4) {
+                    *reinterpret_cast<float4*>(Ks + t * dpad + d + i) = make_float4(kf[i], kf[i + 1], kf[i + 2], kf[i + 3]);
+                    *reinterpret_cast<float4*>(Qs + t * dpad + d + i) = make_float4(qf[i], qf[i + 1], qf[i + 2], qf[i + 3]);
+                }
+            }
+            for (int idx = threadIdx.x; idx < nt * vvecs; idx += blockDim.x) {
+                const int t = idx / vvecs, cc = (idx % vvecs) * VN;
+                float xf[VN];
+                ds_load16<T>(vb + (int64_t)(row0 + t0 + t) * p.v_stride + cc, xf);
+#pragma unroll
+                for (int i = 0; i < VN; ++i)
+                    if (p.act) xf[i] = silu_f32(xf[i]);
+#pragma unroll
+                for (int i = 0; i < VN; i += 4)
+                    *reinterpret_cast<float4*>(Vs + t * ccols + cc + i) = make_float4(xf[i], xf[i + 1], xf[i + 2], xf[i + 3]);
+            }
+        } else {
         for (int idx = threadIdx.x; idx < nt * dpad; idx += blockDim.x) {
             const int t = idx / dpad, d = idx % dpad;
             float qv = 0.f, kv = 0.f;
             if (d < p.dim) {
-                qv = to_f32<T>(qb[(int64_t)(row0 + t0 + t) * p.q_stride + d]);
                 kv = to_f32<T>(kb[(int64_t)(row0 + t0 + t) * p.k_stride + d]);
+                if (MODE != 1) qv = to_f32<T>(qb[(int64_t)(row0 + t0 + t) * p.q_stride + d]);
                 if (p.act) { qv = silu_f32(qv); kv = silu_f32(kv); }
             }
             Qs[idx] = qv;
             Ks[idx] = kv;
         }
+        for (int idx = threadIdx.x; idx < nt * ccols; idx += blockDim.x) {
+            const int t = idx / ccols, cc = idx % ccols;
+            float x = cc < vcols ? to_f32<T>(vb[(int64_t)(row0 + t0 + t) * p.v_stride + cc]) : 0.f;
+            if (p.act) x = silu_f32(x);
+            Vs[idx] = x;
+        }
+        }
         if (threadIdx.x < nt) {
-            float a = hd, s = 1.f;
+            float a = hd, sc = 1.f;
             if (p.dt) {
                 const float raw = to_f32<T>(static_cast<const T*>(p.dt)[(int64_t)(row0 + t0 + threadIdx.x) * p.dt_stride + p.dt_off + h]);
-                s = softplus_f32(raw + dtb);
-                a = expf(a_rate * s);
+                sc = softplus_f32(raw + dtb);
+                a = expf(a_rate * sc);
             }
             As[threadIdx.x] = a;
-            Ss[threadIdx.x] = s;
+            Ss[threadIdx.x] = sc;
         }
         __syncthreads();
         for (int t = 0; t < nt; ++t) {
-            float x = live ? to_f32<T>(vb[(int64_t)(row0 + t0 + t) * p.v_stride + c]) : 0.f;
-            if (p.act) x = silu_f32(x);
-            const float a = As[t], xv = x * Ss[t];
+            const float4 x4 = *reinterpret_cast<const float4*>(Vs + t * ccols + cl);
+            const float a = As[t], sc = Ss[t];
+            const float x[kDsCpt] = {x4.x, x4.y, x4.z, x4.w};
+            float xv[kDsCpt], o[kDsCpt];
+#pragma unroll
+            for (int j = 0; j < kDsCpt; ++j) { xv[j] = x[j] * sc; o[j] = 0.f; }
             const float* kt = Ks + t * dpad + d0;
             const float* qt = Qs + t * dpad + d0;
-            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
             for (int i = 0; i < DPT; i += 4) {
                 const float4 k4 = *reinterpret_cast<const float4*>(kt + i);
-                const float4 q4 = *reinterpret_cast<const float4*>(qt + i);
-                S[i] = fmaf(a, S[i], k4.x * xv);
-                S[i + 1] = fmaf(a, S[i + 1], k4.y * xv);
-                S[i + 2] = fmaf(a, S[i + 2], k4.z * xv);
-                S[i + 3] = fmaf(a, S[i + 3], k4.w * xv);
-                o0 = fmaf(S[i], q4.x, o0);
-                o1 = fmaf(S[i + 1], q4.y, o1);
-                o2 = fmaf(S[i + 2], q4.z, o2);
-                o3 = fmaf(S[i + 3], q4.w, o3);
+                const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
+                float qq[4] = {0.f, 0.f, 0.f, 0.f};
+                if (MODE != 1) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(qt + i);
+                    qq[0] = q4.x; qq[1] = q4.y; qq[2] = q4.z; qq[3] = q4.w;
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int j = 0; j < kDsCpt; ++j) {
+                        S[i + u][j] = fmaf(a, S[i + u][j], kk[u] * xv[j]);
+                        if (MODE != 1) o[j] = fmaf(S[i + u][j], qq[u], o[j]);
+                    }
             }
             total *= a;
-            if (p.mode != 1) {
-                const float o = (o0 + o1) + (o2 + o3);
-                if (NS == 1) {
-                    if (live) p.out[(int64_t)(row0 + t0 + t) * p.out_stride + (int64_t)h * p.vdim + c] = fmaf(skip, x, o);
-                } else {
-                    Ps[(t * NS + slice) * kDsCols + col] = slice == 0 ? fmaf(skip, x, o) : o;
+            if (MODE != 1) {
+                for (int w = 1; w < NSL; w <<= 1)
+#pragma unroll
+                    for (int j = 0; j < kDsCpt; ++j) o[j] += __shfl_xor_sync(0xffffffffu, o[j], w);
+                if (slice == 0) {
+                    float* dst = p.out + (int64_t)(row0 + t0 + t) * p.out_stride + (int64_t)h * p.vdim + c;
+#pragma unroll
+                    for (int j = 0; j < kDsCpt; ++j)
+                        if (c + j < p.vdim) dst[j] = fmaf(skip, x[j], o[j]);
                 }
             }
         }
-        if (NS > 1 && p.mode != 1) {
-            __syncthreads();
-            for (int idx = threadIdx.x; idx < nt * kDsCols; idx += blockDim.x) {
-                const int t = idx / kDsCols, cc = idx % kDsCols;
-                if (blockIdx.z * kDsCols + cc >= p.vdim) continue;
-                float o = 0.f;
-                for (int s = 0; s < NS; ++s) o += Ps[(t * NS + s) * kDsCols + cc];
-                p.out[(int64_t)(row0 + t0 + t) * p.out_stride + (int64_t)h * p.vdim + blockIdx.z * kDsCols + cc] = o;
-            }
-        }
     }
-    if (p.mode == 2) return;
-    float* dst = p.mode == 0 ? p.state + ((int64_t)slot * p.heads + h) * sz : p.part + ((int64_t)blockIdx.x * p.heads + h) * (sz + 1);
-    if (live)
+    if (MODE == 2) return;
+    float* dst = MODE == 0 ? p.state + ((int64_t)slot * p.heads + h) * sz : p.part + ((int64_t)blockIdx.x * p.heads + h) * (sz + 1);
 #pragma unroll
-        for (int i = 0; i < DPT; ++i)
-            if (d0 + i < p.dim) dst[(int64_t)(d0 + i) * p.vdim + c] = S[i];
-    if (p.mode == 1 && threadIdx.x == 0 && blockIdx.z == 0) dst[sz] = total;
+    for (int i = 0; i < DPT; ++i)
+#pragma unroll
+        for (int j = 0; j < kDsCpt; ++j)
+            if (d0 + i < p.dim && c + j < p.vdim) dst[(int64_t)(d0 + i) * p.vdim + c + j] = S[i][j];
+    if (MODE == 1 && threadIdx.x == 0 && blockIdx.z == 0) dst[sz] = total;
 }
 
 // Chain pass of the chunked scan: per (portion, head, state element) walk the portion's chunks in order from the state
@@ -270,26 +336,70 @@ __global__ void __launch_bounds__(256) gated_norm_kernel(const float* __restrict
     }
 }
 
-template <typename T, int DPT>
-static int ds_launch(const DecayScanParams& p, int nitems, int NS, cudaStream_t st) {
-    const size_t smem = ((size_t)2 * kDsTokens * NS * DPT + 2 * kDsTokens + (NS > 1 ? (size_t)kDsTokens * NS * kDsCols : 0)) * sizeof(float);
-    dim3 grid((unsigned)nitems, (unsigned)p.heads, (unsigned)((p.vdim + kDsCols - 1) / kDsCols));
+// the same with one CTA per (row, group): groups of many values, or few rows
+template <typename T>
+__global__ void __launch_bounds__(256) gated_norm_block_kernel(const float* __restrict__ y, int inner, int groups,
+                                                               const T* __restrict__ gate, int64_t gate_stride, int gate_off,
+                                                               int gate_mode, const float* __restrict__ weight, float eps,
+                                                               T* __restrict__ out) {
+    __shared__ float sm[32];
+    const int64_t r = blockIdx.x / groups;
+    const int gsz = inner / groups, c0 = (int)(blockIdx.x % groups) * gsz;
+    const float* yr = y + r * inner + c0;
+    const T* gr = gate ? gate + r * gate_stride + gate_off + c0 : nullptr;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < gsz; j += blockDim.x) {
+        float v = yr[j];
+        if (gate_mode == 1) v *= silu_f32(to_f32<T>(gr[j]));
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, sm);
+    const float rn = 1.0f / sqrtf(ss / (float)gsz + eps);
+    for (int j = threadIdx.x; j < gsz; j += blockDim.x) {
+        float v = yr[j];
+        if (gate_mode == 1) v *= silu_f32(to_f32<T>(gr[j]));
+        v = v * rn * weight[c0 + j];
+        if (gate_mode == 2) v *= sigmoid_f32(to_f32<T>(gr[j]));
+        out[r * inner + c0 + j] = from_f32<T>(v);
+    }
+}
+
+template <typename T, int DPT, int MODE>
+static int ds_launch(const DecayScanParams& p, int nitems, int NSL, cudaStream_t st) {
+    // threads: enough column groups for vdim, whole warps, at most kDsMaxThreads
+    int threads = (p.vdim + kDsCpt - 1) / kDsCpt * NSL;
+    threads = (threads + 31) / 32 * 32;
+    if (threads > kDsMaxThreads) threads = kDsMaxThreads;
+    const int ccols = threads / NSL * kDsCpt;
+    DecayScanParams q = p;
+    {   // 16-byte staging: pointers, row strides, column offsets, dim, vdim and a CTA's share of the columns all whole vectors
+        const int VN = 16 / (int)sizeof(T);
+        auto al = [&](const void* ptr, int64_t stride, int off) {
+            return (uintptr_t)ptr % 16 == 0 && stride % VN == 0 && off % VN == 0;
+        };
+        q.vec = p.dim % VN == 0 && p.vdim % VN == 0 && ccols % VN == 0 && al(p.q, p.q_stride, p.q_off) &&
+                al(p.k, p.k_stride, p.k_off) && al(p.v, p.v_stride, p.v_off);
+    }
+    const size_t smem = ((size_t)2 * kDsTokens * NSL * DPT + (size_t)kDsTokens * ccols + 2 * kDsTokens) * sizeof(float);
+    if (smem > 200 * 1024) return PA_ERR_UNSUPPORTED;
+    auto kern = decay_scan_kernel<T, DPT, MODE>;
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(decay_scan_kernel<T, DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    decay_scan_kernel<T, DPT><<<grid, kDsCols * NS, smem, st>>>(p);
+    dim3 grid((unsigned)nitems, (unsigned)p.heads, (unsigned)((p.vdim + ccols - 1) / ccols));
+    kern<<<grid, threads, smem, st>>>(q, NSL);
     PA_RETURN_LAUNCH_STATUS();
 }
 
-template <typename T>
+template <typename T, int MODE>
 static int ds_dispatch(const DecayScanParams& p, int nitems, cudaStream_t st) {
-    if (p.dim <= 16) return ds_launch<T, 16>(p, nitems, 1, st);
-    if (p.dim <= 32) return ds_launch<T, 32>(p, nitems, 1, st);
-    if (p.dim <= 64) return ds_launch<T, 64>(p, nitems, 1, st);
-    const int NS = (p.dim + 127) / 128;
-    if (NS > 4) return PA_ERR_UNSUPPORTED;
-    return ds_launch<T, 128>(p, nitems, NS, st);
+    if (p.dim <= 8) return ds_launch<T, 8, MODE>(p, nitems, 1, st);
+    if (p.dim <= 16) return ds_launch<T, 16, MODE>(p, nitems, 1, st);
+    int NSL = 1;
+    while (NSL * 32 < p.dim) NSL <<= 1;
+    if (NSL > 32) return PA_ERR_UNSUPPORTED;
+    return ds_launch<T, 32, MODE>(p, nitems, NSL, st);
 }
 
 }  // namespace pa
@@ -349,7 +459,7 @@ PA_API int pa_decay_scan(const void* d_q, int64_t q_stride, int q_off, const voi
 #define PA_DS(MODE)                                                                                \
     do {                                                                                           \
         p.mode = MODE;                                                                             \
-        const int rc = elem == 4 ? ds_dispatch<float>(p, num_items, st) : ds_dispatch<bf16_t>(p, num_items, st); \
+        const int rc = elem == 4 ? ds_dispatch<float, MODE>(p, num_items, st) : ds_dispatch<bf16_t, MODE>(p, num_items, st); \
         if (rc != PA_OK) return rc;                                                                \
     } while (0)
     if (!chunked) {
@@ -373,6 +483,12 @@ PA_API int pa_gated_rms_norm(const float* d_y, int64_t rows, int inner, int grou
     PA_CHECK_ARG(d_y && d_weight && d_out && rows >= 0 && inner > 0 && groups > 0 && inner % groups == 0);
     PA_CHECK_ARG(gate_mode >= 0 && gate_mode <= 2 && (gate_mode == 0 || d_gate));
     if (rows == 0) return PA_OK;
+    if (inner / groups >= 512 && rows * groups < (1 << 30)) {
+        PA_DISPATCH_ELEM(elem, gated_norm_block_kernel<T><<<(unsigned)(rows * groups), 256, 0, as_stream(stream)>>>(
+                                   d_y, inner, groups, static_cast<const T*>(d_gate), gate_stride, gate_off, gate_mode, d_weight,
+                                   eps, static_cast<T*>(d_out)));
+        PA_RETURN_LAUNCH_STATUS();
+    }
     const int64_t threads = rows * groups * 32;
     PA_DISPATCH_ELEM(elem, gated_norm_kernel<T><<<(unsigned)((threads + 255) / 256), 256, 0, as_stream(stream)>>>(
                                d_y, rows, inner, groups, static_cast<const T*>(d_gate), gate_stride, gate_off, gate_mode,

@@ -744,7 +744,7 @@ def test_gated_group_norm_kernel_alone():
     from llm_decoder import _cabi
     lib, dev = _cabi.lib(), torch.device("cuda")
     g = torch.Generator().manual_seed(6)
-    for inner, groups in ((96, 2), (70, 1), (120, 5), (33, 3)):
+    for inner, groups in ((96, 2), (70, 1), (120, 5), (33, 3), (1100, 2), (2048, 1)):
         y, gate, w = torch.randn(9, inner, generator=g) * 3, torch.randn(9, inner + 7, generator=g), torch.randn(inner, generator=g)
         for mode in (0, 1, 2):
             out = torch.empty(9, inner, dtype=torch.float32, device=dev)
@@ -757,7 +757,7 @@ def test_gated_group_norm_kernel_alone():
             want = R.rms(yy.reshape(9, groups, inner // groups), 1e-6).reshape(9, inner) * w.double()
             if mode == 2:
                 want = want * torch.sigmoid(gg)
-            assert (out.double().cpu() - want).abs().max() < 1e-5
+            assert (out.double().cpu() - want).abs().max() < 2e-5
 
 
 # ---- the command-line programs -------------------------------------------------------------------------------------------
