@@ -231,9 +231,9 @@ static int ma_dispatch(const MaskAttnParams& p, int ntiles, cudaStream_t st) {
 
 // ---- single-token tiles (decode) ------------------------------------------------------------------------------------
 // One CTA = one token x one key/value head; its R >= heads-per-kv-head rows are the query heads of the group.  Nothing is
-// staged: each of the 8 warps takes every 8th run of 32 keys of the visible range, a lane reads ITS key's row with 16-byte
+// staged: each of the kMaDecWarps warps takes every kMaDecWarps-th run of 32 keys of the visible range, a lane reads ITS key's row with 16-byte
 // loads straight into the dot products of every row (queries broadcast from shared memory), the warp does the online
-// softmax, then lanes switch to value columns and read each key's value row coalesced.  The 8 warps' (m, l, acc) are
+// softmax, then lanes switch to value columns and read each key's value row coalesced.  The warps' (m, l, acc) are
 // merged through shared memory.  Needs dim a multiple of the 16-byte vector and R <= 8 (else the tile kernel serves).
 template <typename T> struct MaVec { static constexpr int N = 16 / sizeof(T); };
 
@@ -252,8 +252,10 @@ __device__ __forceinline__ void ma_load16(const T* __restrict__ p, float (&f)[Ma
     }
 }
 
+constexpr int kMaDecWarps = 16;   // a window of ~1000 keys leaves each warp two steps: the chain of dependent loads stays short
+
 template <typename T, int R, int NV>
-__global__ void __launch_bounds__(kMaWarps * 32) masked_attention_decode_kernel(const MaskAttnParams p) {
+__global__ void __launch_bounds__(kMaDecWarps * 32) masked_attention_decode_kernel(const MaskAttnParams p) {
     extern __shared__ float smem[];
     constexpr int VN = MaVec<T>::N;
     const int kd = p.dim;
@@ -284,7 +286,7 @@ __global__ void __launch_bounds__(kMaWarps * 32) masked_attention_decode_kernel(
     const int first = ma_first_key(p, pos), total = pos + 1;
     const int s_begin = first / kMaKeys, s_end = (total + kMaKeys - 1) / kMaKeys;
     const int32_t* trow = p.table + ((int64_t)slot * p.num_kv_heads + g) * p.num_tiles;
-    for (int st = s_begin + warp; st < s_end; st += kMaWarps) {
+    for (int st = s_begin + warp; st < s_end; st += kMaDecWarps) {
         const int j = st * kMaKeys + lane;
         int prow = -1;                                  // pool row of this lane's key
         if (j >= first && j < total && j / p.tile_size < p.num_tiles) {
@@ -296,7 +298,7 @@ __global__ void __launch_bounds__(kMaWarps * 32) masked_attention_decode_kernel(
         for (int r = 0; r < R; ++r) s[r] = 0.f;
         if (prow >= 0) {
             const T* kr = kp + (int64_t)prow * kd;
-#pragma unroll 2
+#pragma unroll 8
             for (int d0 = 0; d0 < kd; d0 += VN) {
                 float kv[VN];
                 ma_load16<T>(kr + d0, kv);
@@ -322,7 +324,7 @@ __global__ void __launch_bounds__(kMaWarps * 32) masked_attention_decode_kernel(
             for (int i = 0; i < NV; ++i) acc[r][i] *= c;
         }
         const int nk = min(kMaKeys, total - st * kMaKeys);
-#pragma unroll 4
+#pragma unroll 8
         for (int jj = 0; jj < nk; ++jj) {
             const int pr = __shfl_sync(0xffffffffu, prow, jj);
             float v[NV];
@@ -351,14 +353,14 @@ __global__ void __launch_bounds__(kMaWarps * 32) masked_attention_decode_kernel(
             if (lane + 32 * i < p.vdim) dst[2 + lane + 32 * i] = acc[r][i];
     }
     __syncthreads();
-    for (int r = warp; r < R; r += kMaWarps) {
+    for (int r = warp; r < R; r += kMaDecWarps) {
         if (r >= hpg) continue;
         float M = -INFINITY;
-        for (int w = 0; w < kMaWarps; ++w) M = fmaxf(M, Ps[((int64_t)w * R + r) * pstride]);
+        for (int w = 0; w < kMaDecWarps; ++w) M = fmaxf(M, Ps[((int64_t)w * R + r) * pstride]);
         float L = 0.f, b[NV];
 #pragma unroll
         for (int i = 0; i < NV; ++i) b[i] = 0.f;
-        for (int w = 0; w < kMaWarps; ++w) {
+        for (int w = 0; w < kMaDecWarps; ++w) {
             const float* pw = Ps + ((int64_t)w * R + r) * pstride;
             const float f = pw[0] == -INFINITY ? 0.f : expf(pw[0] - M);
             L = fmaf(f, pw[1], L);
@@ -376,13 +378,13 @@ __global__ void __launch_bounds__(kMaWarps * 32) masked_attention_decode_kernel(
 
 template <typename T, int R, int NV>
 static int ma_decode_launch(const MaskAttnParams& p, int ntiles, cudaStream_t st) {
-    const size_t smem = ((size_t)R * p.dim + (size_t)kMaWarps * R * (2 + p.vdim)) * sizeof(float);
+    const size_t smem = ((size_t)R * p.dim + (size_t)kMaDecWarps * R * (2 + p.vdim)) * sizeof(float);
     if (smem > 200 * 1024) return PA_ERR_UNSUPPORTED;
     auto kern = masked_attention_decode_kernel<T, R, NV>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((unsigned)ntiles, (unsigned)p.num_kv_heads);
-    kern<<<grid, kMaWarps * 32, smem, st>>>(p);
+    kern<<<grid, kMaDecWarps * 32, smem, st>>>(p);
     PA_RETURN_LAUNCH_STATUS();
 }
 

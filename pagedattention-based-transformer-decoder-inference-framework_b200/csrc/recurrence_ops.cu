@@ -296,11 +296,23 @@ __global__ void __launch_bounds__(256) decay_chunk_chain_kernel(float* __restric
     if (n <= 0) return;
     float* sp = state + ((int64_t)seq_slot[s] * heads + h) * sz + e;
     float S = *sp;
-    for (int k = k0; k < k0 + n; ++k) {
-        float* pk = part + ((int64_t)k * heads + h) * (sz + 1);
-        const float B = pk[e], A = pk[sz];
-        pk[e] = S;
-        S = fmaf(A, S, B);
+    // the folded values of 8 chunks are read before any incoming state is written over them: the loads do not wait on
+    // the chain
+    constexpr int U = 8;
+    for (int k = k0; k < k0 + n; k += U) {
+        float A[U], B[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const bool ok = k + u < k0 + n;
+            const float* pk = part + ((int64_t)(ok ? k + u : k) * heads + h) * (sz + 1);
+            A[u] = ok ? pk[sz] : 1.f;
+            B[u] = ok ? pk[e] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (k + u < k0 + n) part[((int64_t)(k + u) * heads + h) * (sz + 1) + e] = S;
+            S = fmaf(A[u], S, B[u]);
+        }
     }
     *sp = S;
 }
