@@ -252,9 +252,41 @@ __device__ __forceinline__ void ma_load16(const T* __restrict__ p, float (&f)[Ma
     }
 }
 
+// NV consecutive values of a row starting at element lane * NV, in one load where NV * sizeof(T) is 4, 8 or a multiple of 16
+template <typename T, int NV>
+__device__ __forceinline__ void ma_load_packed(const T* __restrict__ p, float (&f)[NV]) {
+    constexpr int BYTES = NV * sizeof(T);
+    if (BYTES % 16 == 0) {
+#pragma unroll
+        for (int c = 0; c < BYTES / 16; ++c) {
+            float t[MaVec<T>::N];
+            ma_load16<T>(p + c * MaVec<T>::N, t);
+#pragma unroll
+            for (int i = 0; i < MaVec<T>::N; ++i) f[c * MaVec<T>::N + i] = t[i];
+        }
+    } else if (BYTES == 8 && sizeof(T) == 2) {
+        const uint2 v = ldg_stream_64(p);
+        f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+        f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+    } else if (BYTES == 8) {
+        const uint2 v = ldg_stream_64(p);
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
+    } else if (BYTES == 4 && sizeof(T) == 2) {
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(p);
+        f[0] = __uint_as_float(v << 16); f[1] = __uint_as_float(v & 0xffff0000u);
+    } else {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) f[i] = to_f32<T>(p[i]);
+    }
+}
+
+// value column held in slot i of a lane: lane + 32 i, or (PACKED: vdim == 32 NV) lane * NV + i
+template <int NV, bool PACKED>
+__device__ __forceinline__ int ma_col(int lane, int i) { return PACKED ? lane * NV + i : lane + 32 * i; }
+
 constexpr int kMaDecWarps = 16;   // a window of ~1000 keys leaves each warp two steps: the chain of dependent loads stays short
 
-template <typename T, int R, int NV>
+template <typename T, int R, int NV, bool PACKED>
 __global__ void __launch_bounds__(kMaDecWarps * 32) masked_attention_decode_kernel(const MaskAttnParams p) {
     extern __shared__ float smem[];
     constexpr int VN = MaVec<T>::N;
@@ -332,8 +364,12 @@ __global__ void __launch_bounds__(kMaDecWarps * 32) masked_attention_decode_kern
             for (int i = 0; i < NV; ++i) v[i] = 0.f;
             if (pr >= 0) {
                 const T* vr = vp + (int64_t)pr * p.vdim;
+                if (PACKED) {
+                    ma_load_packed<T, NV>(vr + lane * NV, v);
+                } else {
 #pragma unroll
-                for (int i = 0; i < NV; ++i) v[i] = lane + 32 * i < p.vdim ? to_f32<T>(vr[lane + 32 * i]) : 0.f;
+                    for (int i = 0; i < NV; ++i) v[i] = lane + 32 * i < p.vdim ? to_f32<T>(vr[lane + 32 * i]) : 0.f;
+                }
             }
 #pragma unroll
             for (int r = 0; r < R; ++r) {
@@ -350,7 +386,7 @@ __global__ void __launch_bounds__(kMaDecWarps * 32) masked_attention_decode_kern
         if (lane == 0) { dst[0] = m[r]; dst[1] = l[r]; }
 #pragma unroll
         for (int i = 0; i < NV; ++i)
-            if (lane + 32 * i < p.vdim) dst[2 + lane + 32 * i] = acc[r][i];
+            if (ma_col<NV, PACKED>(lane, i) < p.vdim) dst[2 + ma_col<NV, PACKED>(lane, i)] = acc[r][i];
     }
     __syncthreads();
     for (int r = warp; r < R; r += kMaDecWarps) {
@@ -366,13 +402,13 @@ __global__ void __launch_bounds__(kMaDecWarps * 32) masked_attention_decode_kern
             L = fmaf(f, pw[1], L);
 #pragma unroll
             for (int i = 0; i < NV; ++i)
-                if (lane + 32 * i < p.vdim) b[i] = fmaf(f, pw[2 + lane + 32 * i], b[i]);
+                if (ma_col<NV, PACKED>(lane, i) < p.vdim) b[i] = fmaf(f, pw[2 + ma_col<NV, PACKED>(lane, i)], b[i]);
         }
         T* dst = static_cast<T*>(p.out) + (int64_t)row0 * p.heads * p.vdim + (int64_t)(g * hpg + r) * p.vdim;
         const float inv = 1.0f / L;
 #pragma unroll
         for (int i = 0; i < NV; ++i)
-            if (lane + 32 * i < p.vdim) dst[lane + 32 * i] = from_f32<T>(b[i] * inv);
+            if (ma_col<NV, PACKED>(lane, i) < p.vdim) dst[ma_col<NV, PACKED>(lane, i)] = from_f32<T>(b[i] * inv);
     }
 }
 
@@ -380,7 +416,10 @@ template <typename T, int R, int NV>
 static int ma_decode_launch(const MaskAttnParams& p, int ntiles, cudaStream_t st) {
     const size_t smem = ((size_t)R * p.dim + (size_t)kMaDecWarps * R * (2 + p.vdim)) * sizeof(float);
     if (smem > 200 * 1024) return PA_ERR_UNSUPPORTED;
-    auto kern = masked_attention_decode_kernel<T, R, NV>;
+    // one load per lane and value row where the row is exactly 32 lanes x NV values and the pool is aligned for it
+    const bool packed = p.vdim == 32 * NV && (uintptr_t)p.v_pool % 16 == 0 &&
+                        ((NV * sizeof(T)) % 16 == 0 || NV * sizeof(T) == 8 || (NV * sizeof(T) == 4 && sizeof(T) == 2));
+    auto kern = packed ? masked_attention_decode_kernel<T, R, NV, true> : masked_attention_decode_kernel<T, R, NV, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((unsigned)ntiles, (unsigned)p.num_kv_heads);
