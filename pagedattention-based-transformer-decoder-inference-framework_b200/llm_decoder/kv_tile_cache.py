@@ -129,6 +129,34 @@ class KVTileCache:
             self.tile_to_page_map_.move_to_end(key)  # update_lru
             return page
 
+    def register_range(self, beam_id, t0, t1):
+        """register_tile for the tiles [t0, t1) of EVERY head of table row `beam_id`, in one pass under the lock (a
+        prompt portion touches hundreds of tiles per layer).  Pages are handed out in the order the single calls would
+        take them (tile by tile, head by head); anything but the plain case -- a tile already mapped, or too few free
+        pages -- goes through register_tile and fails or evicts as it does."""
+        beam_id, t0, t1 = int(beam_id), int(t0), int(t1)
+        pt = self.page_table_
+        H, T = pt.num_heads_, pt.num_tiles_
+        n = (t1 - t0) * H
+        if n <= 0:
+            return
+        with self.mutex_:
+            m, free = self.tile_to_page_map_, self._free
+            plain = len(free) >= n and 0 <= t0 and t1 <= T and 0 <= beam_id < pt.num_beams_ and \
+                not any((beam_id, h, t) in m for t in (t0, t1 - 1) for h in range(H))
+            if plain:
+                pages = [free.pop() for _ in range(n)]
+                m.update(zip(((beam_id, h, t) for t in range(t0, t1) for h in range(H)), pages))
+                for h in range(H):
+                    base = (beam_id * H + h) * T
+                    mine = pages[h::H]
+                    pt.host_table_[base + t0:base + t1] = mine
+                    pt._pending.update(zip(range(base + t0, base + t1), mine))
+                return
+        for t in range(t0, t1):
+            for h in range(H):
+                self.register_tile(beam_id, h, t)
+
     def _evict_if_needed(self):
         while self.evict_on_exhaustion and not self._free and self.tile_to_page_map_:
             last, page = self.tile_to_page_map_.popitem(last=False)  # least recently used

@@ -155,9 +155,7 @@ class SequenceStateCache:
         if t1 > self.max_tiles:
             raise RuntimeError("SequenceStateCache: request exceeds the pool")
         for kvc in self._kv:
-            for t in range(t0, t1):
-                for h in range(kvc.page_table_.num_heads_):
-                    kvc.register_tile(slot, h, t)
+            kvc.register_range(slot, t0, t1)
         self._len[slot] = pos0 + n_new
         return pos0
 
