@@ -169,11 +169,20 @@ class KVTileCache:
         loses this reference).  Returns the number of tiles released."""
         beam_id = int(beam_id)
         with self.mutex_:
-            keys = [k for k in self.tile_to_page_map_ if k[0] == beam_id]
-            for k in keys:
-                page = self.tile_to_page_map_.pop(k)
-                self.page_table_.remove(*k)
-                self._release_page(page)
+            m, pt, refs, free = self.tile_to_page_map_, self.page_table_, self._refs(), self._free
+            keys = [k for k in m if k[0] == beam_id]
+            HT, T, host, pend = pt.num_heads_ * pt.num_tiles_, pt.num_tiles_, pt.host_table_, pt._pending
+            for k in keys:                          # PageTable.remove and _release_page, without the calls
+                page = m.pop(k)
+                idx = k[0] * HT + k[1] * T + k[2]
+                host[idx] = -1
+                pend[idx] = -1
+                n = refs.get(page, 1) - 1
+                if n <= 0:
+                    refs.pop(page, None)
+                    free.append(page)
+                else:
+                    refs[page] = n
         return len(keys)
 
     def free_pages(self):
