@@ -630,7 +630,8 @@ def test_causal_convolution_kernel_alone(taps):
 def test_attention_kernels_alone(heads, kv_heads, dim, vdim, mask, size, bias):
     """The float tile kernel, the streaming single-token kernel and the tensor-core kernel over the same paged pool
     (pages handed out in a scattered order) against softmax attention written out in float64: a 150-token portion that
-    starts at position 70 of its sequence, and single tokens at positions 0, 63, 64 and 219 of three others."""
+    starts at position 70 of its sequence, a first token, a two-token portion at positions 63 and 64, and a single token at
+    position 219 of three others."""
     from llm_decoder import _cabi
     from llm_decoder.hybrid import MASK_KIND, log_distance_bucket
     from llm_decoder.seq_state import SequenceStateCache
@@ -639,7 +640,7 @@ def test_attention_kernels_alone(heads, kv_heads, dim, vdim, mask, size, bias):
     per = heads // kv_heads
     scale, cap = dim ** -0.5 * 2.0, 6.0 if bias == "bucket" else 0.0
     ctx = [70, 0, 63, 219]                                  # tokens already cached per sequence
-    new = [150, 1, 2, 1]                                    # tokens of this step (the third: two single-token steps' worth)
+    new = [150, 1, 2, 1]                                    # tokens of this step
     for dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 2e-2)):
         states = SequenceStateCache(4, 1024, 16, dev)
         kv = states.add_kv_layer(kv_heads, dim, vdim, "f32" if dtype == torch.float32 else "bf16")
