@@ -403,6 +403,29 @@ def test_long_portion_and_long_decoding(dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_portion_beside_short_ones(dtype):
+    """One step holds a 300-token portion (which switches the matrix-state scan of the WHOLE batch to its chunked form), a
+    decoded token of a running request, a 2-token portion and a 70-token portion that continues a request."""
+    import llm_decoder as ld
+    config, W = _case("full")
+    reqs = {r: _tokens(n, config["vocab"], 70 + i) for i, (r, n) in enumerate([("a", 330), ("b", 41), ("c", 2), ("d", 100)])}
+    plan = [[("b", 40), ("d", 30)], [("a", 300), ("b", 1), ("c", 2), ("d", 70)], [("a", 30)]]
+    eng = ld.Engine(_model(config, W, dtype))
+    at, got = {r: 0 for r in reqs}, {r: [] for r in reqs}
+    for step in plan:
+        out = eng.step([(r, reqs[r][at[r]:at[r] + n], list(range(n))) for r, n in step])
+        o = 0
+        for r, n in step:
+            got[r].append(out[o:o + n])
+            at[r] += n
+            o += n
+    for r in reqs:
+        assert at[r] == len(reqs[r])
+        _close(torch.cat(got[r], 0), _oracle("full", config, W, reqs[r]), dtype, tol=1.5e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_scheduler(dtype):
     """Scheduler: five prompts of unequal length on four slots with a small token budget (chunked prompts, continuous
     batching, slot reuse); greedy tokens equal the oracle's argmax at every step (float32), and the teacher-forced
