@@ -51,7 +51,7 @@ class Engine:
             return torch.empty((0, self.model.vocab), dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
             batch = self.states.make_batch(batch_entries)
-            want_rows = torch.tensor(want, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+            want_rows = torch.tensor(want, dtype=torch.int32).to(dev)
             return self.model.forward(batch, want_rows)
 
     def finish(self, rid):

@@ -8,9 +8,16 @@
 
 The pools are sized for `max_tokens` live tokens (each request rounded up to whole tiles), not for the sum of all
 requests: pages and slots are used again, and running out is an error, never an eviction of a live request."""
+import numpy as np
 import torch
 
 from .kv_tile_cache import KVTileCache
+
+
+def _to_device(t, device):
+    """A small host tensor of one step's batch description onto the device.  From pageable memory: pinning a fresh buffer
+    per tensor costs a host allocation each (hundreds of microseconds), far more than these few kilobytes take to copy."""
+    return t.to(device) if device.type == "cuda" else t
 
 
 class RaggedBatch:
@@ -19,14 +26,14 @@ class RaggedBatch:
 
     def __init__(self, ids, row_slot, row_pos, row_prev, seq_start, seq_len, seq_slot, portions, device):
         i32 = dict(dtype=torch.int32)
-        host = torch.tensor([ids, row_slot, row_pos, row_prev], **i32)
+        host = torch.from_numpy(np.stack([np.asarray(a, dtype=np.int32) for a in (ids, row_slot, row_pos, row_prev)]))
         self.rows = len(ids)
         self.num_seqs = len(seq_start)
         self.portions = portions                      # host list of (first row, length, slot, first position)
-        dev_rows = host.pin_memory().to(device, non_blocking=True) if device.type == "cuda" else host
+        dev_rows = _to_device(host, device)
         self.ids, self.row_slot, self.row_pos, self.row_prev = dev_rows[0], dev_rows[1], dev_rows[2], dev_rows[3]
         seqs = torch.tensor([seq_start, seq_len, seq_slot], **i32)
-        dev_seqs = seqs.pin_memory().to(device, non_blocking=True) if device.type == "cuda" else seqs
+        dev_seqs = _to_device(seqs, device)
         self.seq_start, self.seq_len, self.seq_slot = dev_seqs[0], dev_seqs[1], dev_seqs[2]
         self.device = device
         self._cache = {}
@@ -51,8 +58,7 @@ class RaggedBatch:
                     out[kind] = None
                     continue
                 t = torch.tensor(tiles, dtype=torch.int32).reshape(-1, 4)
-                t = t.pin_memory().to(self.device, non_blocking=True) if self.device.type == "cuda" else t
-                out[kind] = (t, len(tiles), max(p + m for _r, m, _s, p in tiles))
+                out[kind] = (_to_device(t, self.device), len(tiles), max(p + m for _r, m, _s, p in tiles))
             self._cache[key] = out
         return self._cache[key]
 
@@ -71,8 +77,7 @@ class RaggedBatch:
                 sn.append(len(items) - s0[-1])
             t = torch.tensor(items, dtype=torch.int32).reshape(-1, 4)
             b = torch.tensor([s0, sn], dtype=torch.int32)
-            if self.device.type == "cuda":
-                t, b = t.pin_memory().to(self.device, non_blocking=True), b.pin_memory().to(self.device, non_blocking=True)
+            t, b = _to_device(t, self.device), _to_device(b, self.device)
             self._cache[key] = (t, len(items), b[0], b[1])
         return self._cache[key]
 
@@ -90,8 +95,7 @@ class RaggedBatch:
                 sn.append(len(cs) - s0[-1])
             a = torch.tensor([cs, cl], dtype=torch.int32)
             b = torch.tensor([s0, sn], dtype=torch.int32)
-            if self.device.type == "cuda":
-                a, b = a.pin_memory().to(self.device, non_blocking=True), b.pin_memory().to(self.device, non_blocking=True)
+            a, b = _to_device(a, self.device), _to_device(b, self.device)
             self._cache[key] = (a[0], a[1], b[0], b[1], len(cs))
         return self._cache[key]
 
@@ -169,9 +173,10 @@ class SequenceStateCache:
     def make_batch(self, entries):
         """entries: [(slot, token ids)] in batch order, each slot at most once.  Extends every slot by its tokens and
         returns the RaggedBatch."""
-        ids, row_slot, row_pos, row_prev = [], [], [], []
+        ids, row_slot, row_pos, row_prev = [], [], [], []          # one int32 array per portion
         seq_start, seq_len, seq_slot, portions = [], [], [], []
         seen = set()
+        r0 = 0
         for slot, toks in entries:
             if slot in seen:
                 raise ValueError("a sequence may appear once per step")
@@ -180,13 +185,26 @@ class SequenceStateCache:
             if n == 0:
                 continue
             p0 = self.extend(slot, n)
-            r0 = len(ids)
             seq_start.append(r0)
             seq_len.append(n)
             seq_slot.append(slot)
             portions.append((r0, n, slot, p0))
-            ids.extend(int(t) for t in toks)
-            row_slot.extend([slot] * n)
-            row_pos.extend(range(p0, p0 + n))
-            row_prev.extend([-1] + list(range(r0, r0 + n - 1)))
+            if n < 16:      # decoded tokens and short portions: plain lists (an array per field would cost more than it saves)
+                ids.append([int(t) for t in toks])
+                row_slot.append([slot] * n)
+                row_pos.append(list(range(p0, p0 + n)))
+                row_prev.append([-1] + list(range(r0, r0 + n - 1)))
+            else:
+                ids.append(np.asarray(toks, dtype=np.int32))
+                row_slot.append(np.full(n, slot, dtype=np.int32))
+                row_pos.append(np.arange(p0, p0 + n, dtype=np.int32))
+                prev = np.arange(r0 - 1, r0 + n - 1, dtype=np.int32)
+                prev[0] = -1
+                row_prev.append(prev)
+            r0 += n
+        def flat(pieces):
+            if all(isinstance(a, list) for a in pieces):
+                return [v for a in pieces for v in a]
+            return np.concatenate([np.asarray(a, dtype=np.int32) for a in pieces])
+        ids, row_slot, row_pos, row_prev = flat(ids), flat(row_slot), flat(row_pos), flat(row_prev)
         return RaggedBatch(ids, row_slot, row_pos, row_prev, seq_start, seq_len, seq_slot, portions, self.device)
