@@ -14,6 +14,7 @@ import collections
 import torch
 
 from . import _cabi
+from .host_stage import to_device as _to_device
 
 
 class Engine:
@@ -51,7 +52,7 @@ class Engine:
             return torch.empty((0, self.model.vocab), dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
             batch = self.states.make_batch(batch_entries)
-            want_rows = torch.tensor(want, dtype=torch.int32).to(dev)
+            want_rows = _to_device(torch.tensor(want, dtype=torch.int32), dev)
             return self.model.forward(batch, want_rows)
 
     def finish(self, rid):

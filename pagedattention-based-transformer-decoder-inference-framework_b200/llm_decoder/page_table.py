@@ -11,6 +11,7 @@ import numpy as np
 import torch
 
 from . import _cabi
+from .host_stage import to_device
 
 
 class PageTable:
@@ -84,8 +85,9 @@ class PageTable:
         if not self._pending:
             return
         dev = self.d_table_.device
-        idx = torch.tensor(list(self._pending.keys()), dtype=torch.int32).to(dev)
-        pg = torch.tensor(list(self._pending.values()), dtype=torch.int32).to(dev)
+        # through the pinned staging buffer: a copy from pageable memory would wait for everything queued on the stream
+        idx = to_device(torch.tensor(list(self._pending.keys()), dtype=torch.int32), dev)
+        pg = to_device(torch.tensor(list(self._pending.values()), dtype=torch.int32), dev)
         self._pending.clear()
         with torch.cuda.device(dev):
             _cabi.check(_cabi.lib().pa_page_table_update(self.d_table_.data_ptr(), self.total_entries_,

@@ -11,13 +11,8 @@ requests: pages and slots are used again, and running out is an error, never an 
 import numpy as np
 import torch
 
+from .host_stage import to_device as _to_device
 from .kv_tile_cache import KVTileCache
-
-
-def _to_device(t, device):
-    """A small host tensor of one step's batch description onto the device.  From pageable memory: pinning a fresh buffer
-    per tensor costs a host allocation each (hundreds of microseconds), far more than these few kilobytes take to copy."""
-    return t.to(device) if device.type == "cuda" else t
 
 
 class RaggedBatch:
