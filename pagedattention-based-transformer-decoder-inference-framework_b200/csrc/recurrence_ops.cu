@@ -104,7 +104,6 @@ struct DecayScanParams {
 };
 
 constexpr int kDsTokens = 16;                         // tokens staged per step
-constexpr int kDsCpt = 4;                             // value columns per thread
 constexpr int kDsMaxThreads = 128;
 
 __device__ __forceinline__ float softplus_f32(float z) { return z > 20.f ? z : log1pf(expf(z)); }
@@ -124,36 +123,36 @@ __device__ __forceinline__ void ds_load16(const T* __restrict__ p, float (&f)[16
     }
 }
 
-// A thread keeps a DPT x kDsCpt block of the state in registers: lane = (column group) * NSL + (row slice), so the NSL
+// A thread keeps a DPT x CPT block of the state in registers: lane = (column group) * NSL + (row slice), so the NSL
 // threads that share a column group cover NSL * DPT >= dim rows and their partial outputs meet in a shuffle reduction.
 // q, k, v, the decays and the input scales of kDsTokens tokens are staged in shared memory per step (one 16-byte read of
-// q and of k feeds 4 x kDsCpt updates and as many output terms).  MODE 0: a portion from / to its state slot; 1: fold a
+// q and of k feeds 4 x CPT updates and as many output terms).  MODE 0: a portion from / to its state slot; 1: fold a
 // chunk from a zero state into part[item] (no outputs); 2: replay a chunk from part[item] (no state written).
-template <typename T, int DPT, int MODE>
+template <typename T, int DPT, int MODE, int CPT>
 __global__ void __launch_bounds__(kDsMaxThreads) decay_scan_kernel(const DecayScanParams p, int NSL) {
     extern __shared__ __align__(16) float ds_smem[];
     const int dpad = NSL * DPT;
-    const int ccols = blockDim.x / NSL * kDsCpt;       // value columns of this CTA
+    const int ccols = blockDim.x / NSL * CPT;       // value columns of this CTA
     float* Qs = ds_smem;                               // [kDsTokens][dpad]
     float* Ks = Qs + kDsTokens * dpad;                 // [kDsTokens][dpad]
     float* Vs = Ks + kDsTokens * dpad;                 // [kDsTokens][ccols]
     float* As = Vs + kDsTokens * ccols;                // [kDsTokens] decay
     float* Ss = As + kDsTokens;                        // [kDsTokens] input scale
     const int slice = threadIdx.x % NSL, cgrp = threadIdx.x / NSL;
-    const int h = blockIdx.y, cl = cgrp * kDsCpt, c = blockIdx.z * ccols + cl;
+    const int h = blockIdx.y, cl = cgrp * CPT, c = blockIdx.z * ccols + cl;
     const int g = h / (p.heads / p.groups);
     const int* it = p.items + 4 * blockIdx.x;
     const int row0 = it[0], n = it[1], slot = it[2];
     const int d0 = slice * DPT;
     const int64_t sz = (int64_t)p.dim * p.vdim;
 
-    float S[DPT][kDsCpt];
+    float S[DPT][CPT];
     const float* src = MODE == 0 ? p.state + ((int64_t)slot * p.heads + h) * sz
                      : MODE == 2 ? p.part + ((int64_t)blockIdx.x * p.heads + h) * (sz + 1) : nullptr;
 #pragma unroll
     for (int i = 0; i < DPT; ++i)
 #pragma unroll
-        for (int j = 0; j < kDsCpt; ++j)
+        for (int j = 0; j < CPT; ++j)
             S[i][j] = (MODE != 1 && d0 + i < p.dim && c + j < p.vdim) ? src[(int64_t)(d0 + i) * p.vdim + c + j] : 0.f;
     float total = 1.f;                                 // product of the decays (MODE 1)
     const float hd = p.dt ? 0.f : p.decay[h];
@@ -234,12 +233,18 @@ __global__ void __launch_bounds__(kDsMaxThreads) decay_scan_kernel(const DecaySc
         }
         __syncthreads();
         for (int t = 0; t < nt; ++t) {
-            const float4 x4 = *reinterpret_cast<const float4*>(Vs + t * ccols + cl);
             const float a = As[t], sc = Ss[t];
-            const float x[kDsCpt] = {x4.x, x4.y, x4.z, x4.w};
-            float xv[kDsCpt], o[kDsCpt];
+            float x[CPT];
+            if (CPT == 4) {
+                const float4 x4 = *reinterpret_cast<const float4*>(Vs + t * ccols + cl);
+                x[0] = x4.x; x[1] = x4.y; x[CPT - 2] = x4.z; x[CPT - 1] = x4.w;
+            } else {
+                const float2 x2 = *reinterpret_cast<const float2*>(Vs + t * ccols + cl);
+                x[0] = x2.x; x[1] = x2.y;
+            }
+            float xv[CPT], o[CPT];
 #pragma unroll
-            for (int j = 0; j < kDsCpt; ++j) { xv[j] = x[j] * sc; o[j] = 0.f; }
+            for (int j = 0; j < CPT; ++j) { xv[j] = x[j] * sc; o[j] = 0.f; }
             const float* kt = Ks + t * dpad + d0;
             const float* qt = Qs + t * dpad + d0;
 #pragma unroll
@@ -254,7 +259,7 @@ __global__ void __launch_bounds__(kDsMaxThreads) decay_scan_kernel(const DecaySc
 #pragma unroll
                 for (int u = 0; u < 4; ++u)
 #pragma unroll
-                    for (int j = 0; j < kDsCpt; ++j) {
+                    for (int j = 0; j < CPT; ++j) {
                         S[i + u][j] = fmaf(a, S[i + u][j], kk[u] * xv[j]);
                         if (MODE != 1) o[j] = fmaf(S[i + u][j], qq[u], o[j]);
                     }
@@ -263,11 +268,11 @@ __global__ void __launch_bounds__(kDsMaxThreads) decay_scan_kernel(const DecaySc
             if (MODE != 1) {
                 for (int w = 1; w < NSL; w <<= 1)
 #pragma unroll
-                    for (int j = 0; j < kDsCpt; ++j) o[j] += __shfl_xor_sync(0xffffffffu, o[j], w);
+                    for (int j = 0; j < CPT; ++j) o[j] += __shfl_xor_sync(0xffffffffu, o[j], w);
                 if (slice == 0) {
                     float* dst = p.out + (int64_t)(row0 + t0 + t) * p.out_stride + (int64_t)h * p.vdim + c;
 #pragma unroll
-                    for (int j = 0; j < kDsCpt; ++j)
+                    for (int j = 0; j < CPT; ++j)
                         if (c + j < p.vdim) dst[j] = fmaf(skip, x[j], o[j]);
                 }
             }
@@ -278,7 +283,7 @@ __global__ void __launch_bounds__(kDsMaxThreads) decay_scan_kernel(const DecaySc
 #pragma unroll
     for (int i = 0; i < DPT; ++i)
 #pragma unroll
-        for (int j = 0; j < kDsCpt; ++j)
+        for (int j = 0; j < CPT; ++j)
             if (d0 + i < p.dim && c + j < p.vdim) dst[(int64_t)(d0 + i) * p.vdim + c + j] = S[i][j];
     if (MODE == 1 && threadIdx.x == 0 && blockIdx.z == 0) dst[sz] = total;
 }
@@ -376,13 +381,13 @@ __global__ void __launch_bounds__(256) gated_norm_block_kernel(const float* __re
     }
 }
 
-template <typename T, int DPT, int MODE>
+template <typename T, int DPT, int MODE, int CPT>
 static int ds_launch(const DecayScanParams& p, int nitems, int NSL, cudaStream_t st) {
     // threads: enough column groups for vdim, whole warps, at most kDsMaxThreads
-    int threads = (p.vdim + kDsCpt - 1) / kDsCpt * NSL;
+    int threads = (p.vdim + CPT - 1) / CPT * NSL;
     threads = (threads + 31) / 32 * 32;
     if (threads > kDsMaxThreads) threads = kDsMaxThreads;
-    const int ccols = threads / NSL * kDsCpt;
+    const int ccols = threads / NSL * CPT;
     DecayScanParams q = p;
     {   // 16-byte staging: pointers, row strides, column offsets, dim, vdim and a CTA's share of the columns all whole vectors
         const int VN = 16 / (int)sizeof(T);
@@ -394,7 +399,7 @@ static int ds_launch(const DecayScanParams& p, int nitems, int NSL, cudaStream_t
     }
     const size_t smem = ((size_t)2 * kDsTokens * NSL * DPT + (size_t)kDsTokens * ccols + 2 * kDsTokens) * sizeof(float);
     if (smem > 200 * 1024) return PA_ERR_UNSUPPORTED;
-    auto kern = decay_scan_kernel<T, DPT, MODE>;
+    auto kern = decay_scan_kernel<T, DPT, MODE, CPT>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -404,17 +409,19 @@ static int ds_launch(const DecayScanParams& p, int nitems, int NSL, cudaStream_t
     PA_RETURN_LAUNCH_STATUS();
 }
 
-// States of up to 64 rows: 16 rows per thread (64 state registers, about twice the resident warps of 32 rows; measured
-// 1.3x faster at 64 rows).  Larger ones: 32 rows per thread (at 128 rows the wider shuffle reduction of 8 slices costs
-// what the occupancy gains).
+// A thread's block of the state is DPT rows x CPT columns.  States of up to 64 rows: 16 x 4 (64 state registers, about
+// twice the resident warps of 32 x 4; measured 1.3x faster at 64 rows).  Larger ones: 32 x 4.  Measured at 128 rows x 64
+// columns: 16 x 4 (eight row slices, a three-round shuffle reduction) the same time, 32 x 2 (twice the warps, but twice
+// the shared-memory operand reads per update) 1.6x slower -- the kernel is bound by those reads and the shuffles, so the
+// block that feeds the most updates per read wins.
 template <typename T, int MODE>
 static int ds_dispatch(const DecayScanParams& p, int nitems, cudaStream_t st) {
-    if (p.dim <= 8) return ds_launch<T, 8, MODE>(p, nitems, 1, st);
-    if (p.dim <= 64) return ds_launch<T, 16, MODE>(p, nitems, p.dim <= 16 ? 1 : p.dim <= 32 ? 2 : 4, st);
+    if (p.dim <= 8) return ds_launch<T, 8, MODE, 4>(p, nitems, 1, st);
+    if (p.dim <= 64) return ds_launch<T, 16, MODE, 4>(p, nitems, p.dim <= 16 ? 1 : p.dim <= 32 ? 2 : 4, st);
     int NSL = 4;
     while (NSL * 32 < p.dim) NSL <<= 1;
     if (NSL > 32) return PA_ERR_UNSUPPORTED;
-    return ds_launch<T, 32, MODE>(p, nitems, NSL, st);
+    return ds_launch<T, 32, MODE, 4>(p, nitems, NSL, st);
 }
 
 }  // namespace pa
