@@ -731,6 +731,43 @@ int pa_masked_attention(const void* d_q, int64_t q_stride, int q_off, const void
                         int tile_size, const int32_t* d_q_tiles, int num_q_tiles, int heads, int dim, int vdim,
                         float scale, float softcap, int mask_kind, int mask_size, int bias_kind, const float* d_bias,
                         int bias_len, void* d_out, int elem, int tile_kind, pa_stream_t stream);
+/* pa_masked_attention with a temperature per head, a sink and turned values: score *= d_head_scale[h] right after the
+ * scale (NULL: none); mask_kind 1 with mask_keep > 0 also keeps the first mask_keep positions of the sequence visible;
+ * d_sink [heads] (NULL: none): exp(d_sink[h]) joins head h's softmax denominator (no key, no value; zeros add one to the
+ * denominator); d_out_rot [rows][vdim / 2][cos, sin] (NULL: none; a pa_rope_table over vdim): the neighbouring pairs of
+ * every head's output are turned back by the row's angle, in float, before the result is rounded. */
+int pa_masked_attention_sink(const void* d_q, int64_t q_stride, int q_off, const void* d_k_pool, const void* d_v_pool,
+                             const int32_t* d_table, int num_slots, int num_kv_heads, int num_tiles, int total_pages,
+                             int tile_size, const int32_t* d_q_tiles, int num_q_tiles, int heads, int dim, int vdim,
+                             float scale, float softcap, int mask_kind, int mask_size, int mask_keep, int bias_kind,
+                             const float* d_bias, int bias_len, const float* d_head_scale, const float* d_sink,
+                             const float* d_out_rot, void* d_out, int elem, int tile_kind, pa_stream_t stream);
+
+/* ---- the parallel wiring with two norms, polynomial activation, capped logits, biased choice (seq_ops.cu, moe_ops.cu)
+ * pa_residual_add_norm2: x[r] += y + y2 + sum_k sel_w[r, k] * e_k (every addend optional; y, y2 in the activation
+ *   type); e_k is the float row routed[(r, k)], or, where d_sel_id is given and sel_id[r, k] >= experts, the row
+ *   d_ident[r] (activation type: an identity expert returns the feed-forward's input).  Then next1[r] = x[r] / rms(x[r])
+ *   * d_gain1 and next2[r] = x[r] / rms(x[r]) * d_gain2 (each optional) in the activation type.
+ * pa_poly_norm: out[r] = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 over rows of `ff` values, powers element by element,
+ *   N(u) = u / sqrt(mean(u^2) + eps); d_coef: four floats on the device.
+ * pa_logit_softcap: z <- cap * tanh(scale * z / cap) in place (cap 0: only the scale).
+ * pa_router_topk_biased: pa_router_topk_grouped with d_choice_bias [experts] (NULL: none) added to the scores for the
+ *   choice only; renorm divides the chosen scores by their sum + 1e-20.
+ * pa_causal_conv: pa_causal_conv_silu with the activation chosen (0: none, 1: silu) and an optional bias. */
+int pa_residual_add_norm2(float* d_x, int64_t rows, int width, const void* d_y, const void* d_y2, const float* d_routed,
+                          const float* d_sel_w, const int32_t* d_sel_id, int top, int experts, const void* d_ident,
+                          float eps, const float* d_gain1, void* d_next1, const float* d_gain2, void* d_next2, int elem,
+                          pa_stream_t stream);
+int pa_poly_norm(const void* d_z, int64_t rows, int ff, const float* d_coef, float eps, void* d_out, int elem,
+                 pa_stream_t stream);
+int pa_logit_softcap(float* d_logits, int64_t n, float scale, float cap, pa_stream_t stream);
+int pa_router_topk_biased(const void* d_h, const float* d_w_router, const float* d_bias, const float* d_w_shared_gate,
+                          int rows, int width, int experts, int top, int score_fn, int renorm, int ngroups, int keep,
+                          const float* d_choice_bias, int32_t* d_sel_id, float* d_sel_w, float* d_shared_gate, int elem,
+                          pa_stream_t stream);
+int pa_causal_conv(const void* d_in, int64_t in_stride, int in_off, int channels, int taps, const float* d_weight,
+                   const float* d_bias, int act, const float* d_state, const int32_t* d_chunks, int num_chunks, void* d_out,
+                   int64_t out_stride, int elem, pa_stream_t stream);
 
 /* ---- matrix-state recurrences (recurrence_ops.cu) --------------------------------------------------------------------
  * pa_causal_conv_silu: out[r, c] = silu(bias[c] + sum_i w[c, i] * in(t - (taps - 1 - i))[c]) over the tokens of a

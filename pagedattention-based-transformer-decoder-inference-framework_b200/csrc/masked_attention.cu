@@ -5,9 +5,17 @@
 //   score   s = (q . k) * scale;  softcap > 0: s <- softcap * tanh(s / softcap);  then a distance bias is added:
 //           bias_kind 1: - slope[h] * (i - j)            (one slope per query head)
 //           bias_kind 2: + table[min(i - j, len - 1)][h] (a table over the distance, one column per query head)
-//   mask    mask_kind 0: causal (j <= i);  1: sliding window (0 <= i - j < size);  2: chunks (j <= i and
+//           head_scale != null: s <- s * head_scale[h] right after the scale (a temperature per query head)
+//   mask    mask_kind 0: causal (j <= i);  1: sliding window (0 <= i - j < size), which with mask_keep > 0 also keeps the
+//           first mask_keep positions of the sequence visible (at their true positions);  2: chunks (j <= i and
 //           floor(i / size) == floor(j / size), chunks counted from position 0 of the sequence)
+//   sink    sink != null: exp(sink[h]) joins the softmax denominator of head h (a logit without key or value; zeros
+//           give the "one added to the denominator" form)
+//   output  out_rot != null: [rows][vdim / 2][cos, sin] of the batch rows; the neighbouring pairs (2m, 2m + 1) of every
+//           head's output are turned BACK by the row's angle (values that were cached turned by their own position), in
+//           float, before the result is rounded
 //
+
 // No rotation: positions enter through the bias and the mask only.  Scores, the modifiers, softmax weights and the
 // weighted sums are float; K/V pages are stored in the activation type (float or bfloat16).  Only the key steps a
 // tile's rows can see are visited, so the work per token is bounded by the window or chunk size.
@@ -38,6 +46,10 @@ struct MaskAttnParams {
     int bias_kind, bias_len;
     const float* bias;          // kind 1: [heads]; kind 2: [bias_len][heads]
     void* out;                  // [rows][heads * vdim]
+    const float* head_scale;    // [heads] or null
+    const float* sink;          // [heads] or null
+    int mask_keep;              // window masks: the first mask_keep positions stay visible
+    const float* out_rot;       // [rows][vdim / 2][2] or null
     int head_rows;              // tensor-core kernel: every tile is ONE token and the rows are the heads of a kv head
 };
 
@@ -49,14 +61,47 @@ __device__ __forceinline__ int ma_first_key(const MaskAttnParams& p, int pos) {
 
 __device__ __forceinline__ bool ma_visible(const MaskAttnParams& p, int i, int j) {
     if (j > i) return false;
-    if (p.mask_kind == 1) return i - j < p.mask_size;
+    if (p.mask_kind == 1) return i - j < p.mask_size || j < p.mask_keep;
     if (p.mask_kind == 2) return i / p.mask_size == j / p.mask_size;
     return true;
+}
+
+// The key steps (runs of `keys` positions) the rows of a tile can see, in order: the steps of the kept first positions,
+// then the steps from the first key of the tile's first token (ma_first_key) to its last token.  `first` = that first
+// key, `total` = keys up to the tile's last token.
+struct MaSteps {
+    int head, body0, count;
+    __device__ __forceinline__ int step(int n) const { return n < head ? n : body0 + n - head; }
+};
+__device__ __forceinline__ MaSteps ma_steps(const MaskAttnParams& p, int first, int total, int keys) {
+    MaSteps s;
+    s.body0 = first / keys;
+    s.head = 0;
+    if (p.mask_kind == 1 && p.mask_keep > 0) s.head = min(s.body0, (min(p.mask_keep, total) + keys - 1) / keys);
+    s.count = s.head + (total + keys - 1) / keys - s.body0;
+    return s;
+}
+
+// the softmax denominator with the sink of head h: returns the factor for the accumulated sums (and updates l)
+__device__ __forceinline__ float ma_sink(const MaskAttnParams& p, int h, float m, float& l) {
+    if (!p.sink) return 1.f;
+    const float sk = p.sink[h];
+    const float n = fmaxf(m, sk);
+    const float c = m == -INFINITY ? 0.f : expf(m - n);
+    l = l * c + expf(sk - n);
+    return c;
+}
+
+// turns the pair (u, v) = columns (2m, 2m + 1) of batch row `row` back by the row's angle; even = this thread holds u
+__device__ __forceinline__ float ma_unturn(const MaskAttnParams& p, int64_t row, int col, float mine, float other) {
+    const float* t = p.out_rot + (row * (p.vdim >> 1) + (col >> 1)) * 2;
+    return (col & 1) ? mine * t[0] - other * t[1] : mine * t[0] + other * t[1];
 }
 
 // the float score of (query position i, key position j, query head h) from the raw dot product
 __device__ __forceinline__ float ma_score(const MaskAttnParams& p, float dot, int i, int j, int h, float slope) {
     float s = dot * p.scale;
+    if (p.head_scale) s *= p.head_scale[h];
     if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
     if (p.bias_kind == 1) s -= slope * (float)(i - j);
     else if (p.bias_kind == 2) s += p.bias[(int64_t)min(i - j, p.bias_len - 1) * p.heads + h];
@@ -118,11 +163,10 @@ __global__ void __launch_bounds__(kMaWarps * 32) masked_attention_kernel(const M
 
     const int last_tok = min(ntok, bq) - 1;
     const int total = pos0 + last_tok + 1;                 // keys any row of the tile may see
-    const int s_begin = ma_first_key(p, pos0) / kMaKeys;
-    const int s_end = (total + kMaKeys - 1) / kMaKeys;
+    const MaSteps steps = ma_steps(p, ma_first_key(p, pos0), total, kMaKeys);
 
-    for (int st = s_begin; st < s_end; ++st) {
-        const int c0 = st * kMaKeys;
+    for (int sn = 0; sn < steps.count; ++sn) {
+        const int c0 = steps.step(sn) * kMaKeys;
         __syncthreads();                                   // the previous step's tiles are consumed (and Qs is written)
         if (threadIdx.x < kMaKeys) {
             const int j = c0 + threadIdx.x;
@@ -192,10 +236,18 @@ __global__ void __launch_bounds__(kMaWarps * 32) masked_attention_kernel(const M
         if (rpos[r] < 0) continue;
         const int row = warp * kMaRpw + r;
         T* dst = static_cast<T*>(p.out) + (int64_t)(row0 + row / hc) * p.heads * p.vdim + (int64_t)rhead[r] * p.vdim;
-        const float inv = 1.0f / l[r];
+        float ll = l[r];
+        const float inv = ma_sink(p, rhead[r], m[r], ll) / ll;
 #pragma unroll
-        for (int i = 0; i < NV; ++i)
-            if (lane + 32 * i < p.vdim) dst[lane + 32 * i] = from_f32<T>(acc[r][i] * inv);
+        for (int i = 0; i < NV; ++i) {
+            const int col = lane + 32 * i;
+            float v = acc[r][i] * inv;
+            if (p.out_rot) {                           // the partner column sits in the neighbouring lane (vdim is even)
+                const float o = __shfl_xor_sync(0xffffffffu, v, 1);
+                if (col < p.vdim) v = ma_unturn(p, row0 + row / hc, col, v, o);
+            }
+            if (col < p.vdim) dst[col] = from_f32<T>(v);
+        }
     }
 }
 
@@ -315,13 +367,14 @@ __global__ void __launch_bounds__(kMaDecWarps * 32) masked_attention_decode_kern
 #pragma unroll
         for (int i = 0; i < NV; ++i) acc[r][i] = 0.f;
     }
-    const int first = ma_first_key(p, pos), total = pos + 1;
-    const int s_begin = first / kMaKeys, s_end = (total + kMaKeys - 1) / kMaKeys;
+    const int total = pos + 1;
+    const MaSteps steps = ma_steps(p, ma_first_key(p, pos), total, kMaKeys);
     const int32_t* trow = p.table + ((int64_t)slot * p.num_kv_heads + g) * p.num_tiles;
-    for (int st = s_begin + warp; st < s_end; st += kMaDecWarps) {
+    for (int sn = warp; sn < steps.count; sn += kMaDecWarps) {
+        const int st = steps.step(sn);
         const int j = st * kMaKeys + lane;
         int prow = -1;                                  // pool row of this lane's key
-        if (j >= first && j < total && j / p.tile_size < p.num_tiles) {
+        if (j < total && ma_visible(p, pos, j) && j / p.tile_size < p.num_tiles) {
             const int page = trow[j / p.tile_size];
             if (page >= 0 && page < p.total_pages) prow = page * p.tile_size + j % p.tile_size;
         }
@@ -393,7 +446,8 @@ __global__ void __launch_bounds__(kMaDecWarps * 32) masked_attention_decode_kern
         if (r >= hpg) continue;
         float M = -INFINITY;
         for (int w = 0; w < kMaDecWarps; ++w) M = fmaxf(M, Ps[((int64_t)w * R + r) * pstride]);
-        float L = 0.f, b[NV];
+        if (p.sink) M = fmaxf(M, p.sink[g * hpg + r]);
+        float L = p.sink ? expf(p.sink[g * hpg + r] - M) : 0.f, b[NV];
 #pragma unroll
         for (int i = 0; i < NV; ++i) b[i] = 0.f;
         for (int w = 0; w < kMaDecWarps; ++w) {
@@ -407,8 +461,18 @@ __global__ void __launch_bounds__(kMaDecWarps * 32) masked_attention_decode_kern
         T* dst = static_cast<T*>(p.out) + (int64_t)row0 * p.heads * p.vdim + (int64_t)(g * hpg + r) * p.vdim;
         const float inv = 1.0f / L;
 #pragma unroll
+        for (int i = 0; i < NV; ++i) b[i] *= inv;
+        if (p.out_rot) {          // the partner column: the neighbouring slot of this lane (packed pairs) or the neighbouring lane
+            float o[NV];
+#pragma unroll
+            for (int i = 0; i < NV; ++i) o[i] = (PACKED && NV > 1) ? b[i ^ 1] : __shfl_xor_sync(0xffffffffu, b[i], 1);
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+                if (ma_col<NV, PACKED>(lane, i) < p.vdim) b[i] = ma_unturn(p, row0, ma_col<NV, PACKED>(lane, i), b[i], o[i]);
+        }
+#pragma unroll
         for (int i = 0; i < NV; ++i)
-            if (ma_col<NV, PACKED>(lane, i) < p.vdim) dst[ma_col<NV, PACKED>(lane, i)] = from_f32<T>(b[i] * inv);
+            if (ma_col<NV, PACKED>(lane, i) < p.vdim) dst[ma_col<NV, PACKED>(lane, i)] = from_f32<T>(b[i]);
     }
 }
 
@@ -485,7 +549,8 @@ __global__ void __launch_bounds__(kMmThreads) masked_attention_mma_kernel(const 
     const bf16_t* vp = static_cast<const bf16_t*>(p.v_pool);
     const int32_t* trow = p.table + ((int64_t)slot * p.num_kv_heads + g) * p.num_tiles;
     const int total = pos0 + ntok;
-    const int kt0 = ma_first_key(p, pos0) / kMmKeys, nkt = (total + kMmKeys - 1) / kMmKeys;
+    const MaSteps steps = ma_steps(p, ma_first_key(p, pos0), total, kMmKeys);
+    const int keep = p.mask_kind == 1 ? p.mask_keep : 0;
     const int dim = p.dim, vdim = p.vdim;
     const bool bias_smem = p.bias_kind == 2 && p.bias_len <= kMmBiasMax;
 
@@ -529,7 +594,7 @@ __global__ void __launch_bounds__(kMmThreads) masked_attention_mma_kernel(const 
     };
 #pragma unroll
     for (int t = 0; t < NST - 1; ++t) {
-        if (kt0 + t < nkt) load_tile(kt0 + t, t);
+        if (t < steps.count) load_tile(steps.step(t), t);
         cp_async_commit();
     }
 
@@ -548,16 +613,17 @@ __global__ void __launch_bounds__(kMmThreads) masked_attention_mma_kernel(const 
     // the warp's rows together see keys [wlo, whi]
     const int wlo = ma_first_key(p, pos0 + rbase), whi = pos0 + min(rbase + 15, ntok - 1);
     const float slope = p.bias_kind == 1 ? p.bias[head] : 0.f;
+    const float hscale = p.head_scale ? p.head_scale[head] : 1.f;
     const float inv_cap = p.softcap > 0.f ? 1.0f / p.softcap : 0.f;
     constexpr float kLog2e = 1.4426950408889634f;
 
-    for (int kt = kt0; kt < nkt; ++kt) {
-        const int buf = (kt - kt0) % NST, c0 = kt * kMmKeys;
-        if (kt + NST - 1 < nkt) load_tile(kt + NST - 1, (kt - kt0 + NST - 1) % NST);
+    for (int sn = 0; sn < steps.count; ++sn) {
+        const int buf = sn % NST, c0 = steps.step(sn) * kMmKeys;
+        if (sn + NST - 1 < steps.count) load_tile(steps.step(sn + NST - 1), (sn + NST - 1) % NST);
         cp_async_commit();
         cp_async_wait<NST - 1>();
         __syncthreads();
-        if (active && c0 + kMmKeys - 1 >= wlo && c0 <= whi) {
+        if (active && ((c0 + kMmKeys - 1 >= wlo && c0 <= whi) || c0 < keep)) {
         float s[8][4];
 #pragma unroll
         for (int t = 0; t < 8; ++t)
@@ -586,8 +652,9 @@ __global__ void __launch_bounds__(kMmThreads) masked_attention_mma_kernel(const 
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int i = c >> 1, j = c0 + col + (c & 1);
-                const bool vis = ((c & 1) ? okk.y : okk.x) && j <= rpos[i] && j >= rlo[i];
+                const bool vis = ((c & 1) ? okk.y : okk.x) && j <= rpos[i] && (j >= rlo[i] || j < keep);
                 float v = s[t][c] * p.scale;
+                if (p.head_scale) v *= hscale;
                 if (p.softcap > 0.f) v = p.softcap * ma_tanh(v * inv_cap);
                 if (p.bias_kind == 1) v -= slope * (float)(rpos[i] - j);
                 else if (p.bias_kind == 2 && vis) {
@@ -650,11 +717,25 @@ __global__ void __launch_bounds__(kMmThreads) masked_attention_mma_kernel(const 
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
         const int r = rbase + (lane >> 2) + 8 * i;
         if (r >= ntok) continue;
-        const float inv = 1.0f / l[i];
+        float inv = 1.0f / l[i];
+        if (p.sink) {                                        // the running maximum is in the log2 domain
+            const float sk = p.sink[head] * kLog2e, mn = fmaxf(m[i], sk);
+            const float corr = exp2f(m[i] - mn);
+            inv = corr / (l[i] * corr + exp2f(sk - mn));
+        }
         bf16_t* dst = static_cast<bf16_t*>(p.out) + (int64_t)(row0 + r) * p.heads * vdim + (int64_t)head * vdim + 2 * (lane & 3);
 #pragma unroll
-        for (int t = 0; t < NT; ++t)
-            if (t * 8 < vdim) *reinterpret_cast<uint32_t*>(dst + t * 8) = pack_bf16x2(o[t][2 * i] * inv, o[t][2 * i + 1] * inv);
+        for (int t = 0; t < NT; ++t) {
+            if (t * 8 >= vdim) continue;
+            float u = o[t][2 * i] * inv, v = o[t][2 * i + 1] * inv;
+            if (p.out_rot) {                                 // a thread holds both columns of a pair
+                const int col = t * 8 + 2 * (lane & 3);
+                const float u0 = u;
+                u = ma_unturn(p, row0 + r, col, u0, v);
+                v = ma_unturn(p, row0 + r, col + 1, v, u0);
+            }
+            *reinterpret_cast<uint32_t*>(dst + t * 8) = pack_bf16x2(u, v);
+        }
     }
 }
 
@@ -702,6 +783,19 @@ PA_API int pa_masked_attention(const void* d_q, int64_t q_stride, int q_off, con
                                float scale, float softcap, int mask_kind, int mask_size, int bias_kind,
                                const float* d_bias, int bias_len, void* d_out, int elem, int tile_kind,
                                pa_stream_t stream) {
+    return pa_masked_attention_sink(d_q, q_stride, q_off, d_k_pool, d_v_pool, d_table, num_slots, num_kv_heads, num_tiles,
+                                    total_pages, tile_size, d_q_tiles, num_q_tiles, heads, dim, vdim, scale, softcap,
+                                    mask_kind, mask_size, 0, bias_kind, d_bias, bias_len, nullptr, nullptr, nullptr, d_out,
+                                    elem, tile_kind, stream);
+}
+
+PA_API int pa_masked_attention_sink(const void* d_q, int64_t q_stride, int q_off, const void* d_k_pool, const void* d_v_pool,
+                                    const int32_t* d_table, int num_slots, int num_kv_heads, int num_tiles, int total_pages,
+                                    int tile_size, const int32_t* d_q_tiles, int num_q_tiles, int heads, int dim, int vdim,
+                                    float scale, float softcap, int mask_kind, int mask_size, int mask_keep, int bias_kind,
+                                    const float* d_bias, int bias_len, const float* d_head_scale, const float* d_sink,
+                                    const float* d_out_rot, void* d_out, int elem, int tile_kind, pa_stream_t stream) {
+    PA_CHECK_ARG(mask_keep >= 0 && (mask_keep == 0 || mask_kind == 1) && (!d_out_rot || vdim % 2 == 0));
     PA_CHECK_ARG(d_q && d_k_pool && d_v_pool && d_table && d_q_tiles && d_out && num_q_tiles >= 0);
     PA_CHECK_ARG(num_slots > 0 && num_kv_heads > 0 && num_tiles > 0 && total_pages > 0 && tile_size > 0);
     PA_CHECK_ARG(heads > 0 && heads % num_kv_heads == 0 && dim > 0 && vdim > 0 && softcap >= 0.f);
@@ -714,6 +808,7 @@ PA_API int pa_masked_attention(const void* d_q, int64_t q_stride, int q_off, con
     p.tile_size = tile_size; p.tiles = d_q_tiles; p.heads = heads; p.dim = dim; p.vdim = vdim; p.scale = scale;
     p.softcap = softcap; p.mask_kind = mask_kind; p.mask_size = mask_size; p.bias_kind = bias_kind; p.bias = d_bias;
     p.bias_len = bias_len; p.out = d_out; p.head_rows = 0;
+    p.head_scale = d_head_scale; p.sink = d_sink; p.mask_keep = mask_keep; p.out_rot = d_out_rot;
     if (elem != 4 && elem != 2) return PA_ERR_UNSUPPORTED;
     if (tile_kind == 2) {       // on the tensor cores: tiles of up to pa_masked_attention_mma_tile_tokens tokens
         if (elem != 2) return PA_ERR_UNSUPPORTED;

@@ -21,7 +21,10 @@ namespace pa {
 // One warp per row.  score_fn: 0 = sigmoid, 1 = softmax over the experts, 2 = the largest LOGITS are chosen and the
 // weights are the softmax over the chosen logits only.  Ties go to the lower expert id.  With ngroups > 1 the experts
 // form ngroups equal groups of neighbours, a group's score is its largest score, and only experts of the `keep` best
-// groups (ties: lower group) can be chosen.
+// groups (ties: lower group) can be chosen.  choice_bias (optional, one float per expert) is added to the scores for the
+// CHOICE only: the weights are the chosen experts' scores without it.  renorm divides the weights by their sum (+ 1e-20).
+// The expert ids are not interpreted here: a caller may route over more outputs than it has expert weights (identity
+// experts) and sort only the ids below its expert count.
 // The dot products run over groups of kRtGroup weight vectors (the experts' rows and, last, the shared-expert gate's):
 // a lane takes 16-byte pieces of the token row and multiplies each into the whole group, so the row is read once per
 // group and the weights with 16-byte loads (VEC; rows whose width or alignment does not allow it go element by element).
@@ -47,7 +50,8 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const T* __restrict__ 
                                                           const float* __restrict__ bias,
                                                           const float* __restrict__ w_shared_gate, int rows, int width,
                                                           int experts, int top, int score_fn, int renorm,
-                                                          int ngroups, int keep, int32_t* __restrict__ sel_id, float* __restrict__ sel_w,
+                                                          int ngroups, int keep, const float* __restrict__ choice_bias,
+                                                          int32_t* __restrict__ sel_id, float* __restrict__ sel_w,
                                                           float* __restrict__ shared_gate) {
     extern __shared__ float sc[];                     // [warps][experts]
     constexpr int VN = 16 / sizeof(T);
@@ -133,11 +137,13 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const T* __restrict__ 
         for (int k = 0; k < top; ++k) {
             int best = 0;
             float bv = -INFINITY;
-            for (int e = 0; e < experts; ++e)
-                if (s[e] > bv) { bv = s[e]; best = e; }
+            for (int e = 0; e < experts; ++e) {
+                const float v = choice_bias ? s[e] + choice_bias[e] : s[e];
+                if (v > bv) { bv = v; best = e; }
+            }
             sel_id[(int64_t)row * top + k] = best;
-            sel_w[(int64_t)row * top + k] = bv;
-            total += bv;
+            sel_w[(int64_t)row * top + k] = s[best];
+            total += s[best];
             s[best] = -INFINITY;
         }
         if (score_fn == 2) {                          // softmax over the chosen logits (the first chosen is the largest)
@@ -150,7 +156,7 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const T* __restrict__ 
             }
         }
         if (renorm || score_fn == 2)
-            for (int k = 0; k < top; ++k) sel_w[(int64_t)row * top + k] /= total;
+            for (int k = 0; k < top; ++k) sel_w[(int64_t)row * top + k] /= total + 1e-20f;
     }
 }
 
@@ -611,6 +617,14 @@ PA_API int pa_router_topk_grouped(const void* d_h, const float* d_w_router, cons
                                   const float* d_w_shared_gate, int rows, int width, int experts, int top, int score_fn,
                                   int renorm, int ngroups, int keep, int32_t* d_sel_id, float* d_sel_w,
                                   float* d_shared_gate, int elem, pa_stream_t stream) {
+    return pa_router_topk_biased(d_h, d_w_router, d_bias, d_w_shared_gate, rows, width, experts, top, score_fn, renorm,
+                                 ngroups, keep, nullptr, d_sel_id, d_sel_w, d_shared_gate, elem, stream);
+}
+
+PA_API int pa_router_topk_biased(const void* d_h, const float* d_w_router, const float* d_bias,
+                                 const float* d_w_shared_gate, int rows, int width, int experts, int top, int score_fn,
+                                 int renorm, int ngroups, int keep, const float* d_choice_bias, int32_t* d_sel_id,
+                                 float* d_sel_w, float* d_shared_gate, int elem, pa_stream_t stream) {
     PA_CHECK_ARG(d_h && d_w_router && d_sel_id && d_sel_w && rows >= 0 && width > 0 && experts > 0);
     PA_CHECK_ARG(ngroups >= 1 && ngroups <= 64 && experts % ngroups == 0 && keep >= 1 && keep <= ngroups);
     PA_CHECK_ARG((int64_t)keep * (experts / ngroups) >= top);
@@ -624,7 +638,7 @@ PA_API int pa_router_topk_grouped(const void* d_h, const float* d_w_router, cons
 #define PA_ROUTER(VEC)                                                                                                 \
     PA_DISPATCH_ELEM(elem, (router_topk_kernel<T, VEC><<<(unsigned)((rows + 3) / 4), 128, smem, as_stream(stream)>>>(  \
                                static_cast<const T*>(d_h), d_w_router, d_bias, d_w_shared_gate, rows, width, experts, top, \
-                               score_fn, renorm, ngroups, keep, d_sel_id, d_sel_w, d_shared_gate)))
+                               score_fn, renorm, ngroups, keep, d_choice_bias, d_sel_id, d_sel_w, d_shared_gate)))
     if (vec) PA_ROUTER(true);
     else PA_ROUTER(false);
 #undef PA_ROUTER

@@ -28,7 +28,7 @@ template <typename T>
 __global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ in, int64_t in_stride, int in_off, int channels,
                                                           int taps, const float* __restrict__ w, const float* __restrict__ bias,
                                                           const float* __restrict__ state, const int32_t* __restrict__ chunks,
-                                                          T* __restrict__ out, int64_t out_stride) {
+                                                          T* __restrict__ out, int64_t out_stride, int act) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= channels) return;
     const int* ch = chunks + 4 * blockIdx.y;
@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ 
         float acc = b;
 #pragma unroll
         for (int i = 0; i < kMaxTaps; ++i) acc = fmaf(wt[i], win[i], acc);
-        out[(int64_t)(row0 + t) * out_stride + c] = from_f32<T>(silu_f32(acc));
+        out[(int64_t)(row0 + t) * out_stride + c] = from_f32<T>(act ? silu_f32(acc) : acc);
 #pragma unroll
         for (int i = kMaxTaps - 1; i > 0; --i) win[i] = win[i - 1];
     }
@@ -431,13 +431,20 @@ using namespace pa;
 PA_API int pa_causal_conv_silu(const void* d_in, int64_t in_stride, int in_off, int channels, int taps, const float* d_weight,
                                const float* d_bias, const float* d_state, const int32_t* d_chunks, int num_chunks,
                                void* d_out, int64_t out_stride, int elem, pa_stream_t stream) {
-    PA_CHECK_ARG(d_in && d_weight && d_state && d_chunks && d_out && channels > 0 && num_chunks >= 0);
-    PA_CHECK_ARG(taps >= 1 && taps <= kMaxTaps);
+    return pa_causal_conv(d_in, in_stride, in_off, channels, taps, d_weight, d_bias, 1, d_state, d_chunks, num_chunks, d_out,
+                          out_stride, elem, stream);
+}
+
+PA_API int pa_causal_conv(const void* d_in, int64_t in_stride, int in_off, int channels, int taps, const float* d_weight,
+                          const float* d_bias, int act, const float* d_state, const int32_t* d_chunks, int num_chunks,
+                          void* d_out, int64_t out_stride, int elem, pa_stream_t stream) {
+    PA_CHECK_ARG(d_in && d_weight && (d_state || taps == 1) && d_chunks && d_out && channels > 0 && num_chunks >= 0);
+    PA_CHECK_ARG(taps >= 1 && taps <= kMaxTaps && (act == 0 || act == 1));
     if (num_chunks == 0) return PA_OK;
     dim3 grid((unsigned)((channels + 127) / 128), (unsigned)num_chunks);
     PA_DISPATCH_ELEM(elem, causal_conv_kernel<T><<<grid, 128, 0, as_stream(stream)>>>(
                                static_cast<const T*>(d_in), in_stride, in_off, channels, taps, d_weight, d_bias, d_state,
-                               d_chunks, static_cast<T*>(d_out), out_stride));
+                               d_chunks, static_cast<T*>(d_out), out_stride, act));
     PA_RETURN_LAUNCH_STATUS();
 }
 

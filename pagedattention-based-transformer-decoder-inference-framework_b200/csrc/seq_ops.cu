@@ -17,6 +17,11 @@
 //                             sublayer's operand h = x / rms(x) * gain in the activation type (pre-norm wiring: the
 //                             residual add of one sublayer fused with the norm in front of the next)
 //   concat_rows_kernel        [x | x0] of two float row sets in the activation type (input of a looped block)
+//   residual_add_norm2_kernel  the parallel wiring with two norms: x += the sublayers' outputs (routed experts by weight,
+//                             identity experts = the feed-forward's own input row), then BOTH operands of the next layer,
+//                             x / rms(x) * gain1 and x / rms(x) * gain2, from one mean square
+//   poly_norm_kernel          a N(z) + b N(z^2) + c N(z^3) + e per row, N = division by the root mean square of the row
+//   logit_softcap_kernel      cap * tanh(scale * z / cap) on float logits
 //
 // Norms, the recurrence with its gates, and the residual sum are computed in float whatever the activation type.
 #include "seq_common.cuh"
@@ -398,6 +403,82 @@ __global__ void __launch_bounds__(256) residual_add_prenorm_kernel(float* __rest
     for (int j = threadIdx.x; j < width; j += blockDim.x) next[r * width + j] = from_f32<T>(row[j] * rn * gain[j]);
 }
 
+// One CTA per row.  s = y + y2 (activation type, optional) + sum_k w[r, k] * e_k, where e_k is the float row
+// routed[(r, k)] of a real expert (sel_id < experts) or the row ident[r] itself (an identity expert); x[r] += s; then
+// next1 = x / rms(x) * gain1 and next2 = x / rms(x) * gain2 (each optional) in the activation type.
+template <typename T>
+__global__ void __launch_bounds__(256) residual_add_norm2_kernel(float* __restrict__ x, int width, const T* __restrict__ y,
+                                                                 const T* __restrict__ y2, const float* __restrict__ routed,
+                                                                 const float* __restrict__ sel_w,
+                                                                 const int32_t* __restrict__ sel_id, int top, int experts,
+                                                                 const T* __restrict__ ident, float eps,
+                                                                 const float* __restrict__ gain1, T* __restrict__ next1,
+                                                                 const float* __restrict__ gain2, T* __restrict__ next2) {
+    extern __shared__ float row[];                    // [width]
+    __shared__ float sm[32];
+    const int64_t r = blockIdx.x;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float s = 0.f;
+        if (y) s = to_f32<T>(y[r * width + j]);
+        if (y2) s += to_f32<T>(y2[r * width + j]);
+        if (routed) {
+            float e = 0.f;
+            for (int k = 0; k < top; ++k) {
+                const bool same = sel_id && sel_id[r * top + k] >= experts;
+                const float v = same ? to_f32<T>(ident[r * width + j]) : routed[(r * top + k) * width + j];
+                e = fmaf(sel_w ? sel_w[r * top + k] : 1.0f, v, e);
+            }
+            s += e;
+        }
+        const float v = x[r * width + j] + s;
+        x[r * width + j] = v;
+        row[j] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!next1 && !next2) return;
+    ss = block_sum(ss, sm);
+    const float rn = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float v = row[j] * rn;
+        if (next1) next1[r * width + j] = from_f32<T>(v * gain1[j]);
+        if (next2) next2[r * width + j] = from_f32<T>(v * gain2[j]);
+    }
+}
+
+// One CTA per row of `ff` values: the mean squares of z, z^2 and z^3 in one pass, then the weighted sum.
+template <typename T>
+__global__ void __launch_bounds__(256) poly_norm_kernel(const T* __restrict__ z, int ff, const float* __restrict__ coef,
+                                                        float eps, T* __restrict__ out) {
+    __shared__ float sm[32];
+    const int64_t r = blockIdx.x;
+    const T* zr = z + r * ff;
+    float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    for (int j = threadIdx.x; j < ff; j += blockDim.x) {
+        const float v = to_f32<T>(zr[j]), v2 = v * v;
+        s1 += v2;
+        s2 = fmaf(v2, v2, s2);
+        s3 = fmaf(v2 * v, v2 * v, s3);
+    }
+    s1 = block_sum(s1, sm);
+    s2 = block_sum(s2, sm);
+    s3 = block_sum(s3, sm);
+    const float n = (float)ff;
+    const float a = coef[0] / sqrtf(s1 / n + eps), b = coef[1] / sqrtf(s2 / n + eps), c = coef[2] / sqrtf(s3 / n + eps);
+    const float e = coef[3];
+    for (int j = threadIdx.x; j < ff; j += blockDim.x) {
+        const float v = to_f32<T>(zr[j]), v2 = v * v;
+        out[r * ff + j] = from_f32<T>(a * v + b * v2 + c * (v2 * v) + e);
+    }
+}
+
+__global__ void logit_softcap_kernel(float* __restrict__ z, int64_t n, float scale, float cap) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = z[i] * scale;
+    z[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+}
+
 template <typename T>
 __global__ void concat_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, int64_t rows, int width,
                                    T* __restrict__ out) {
@@ -567,6 +648,38 @@ PA_API int pa_residual_add_prenorm(float* d_x, int64_t rows, int width, const vo
                                d_x, width, static_cast<const T*>(d_y), y_scale, static_cast<const T*>(d_y2), y2_scale,
                                d_routed, d_sel_w, top, static_cast<const T*>(d_shared), d_bias, eps, d_gain,
                                static_cast<T*>(d_next)));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_residual_add_norm2(float* d_x, int64_t rows, int width, const void* d_y, const void* d_y2,
+                                 const float* d_routed, const float* d_sel_w, const int32_t* d_sel_id, int top,
+                                 int experts, const void* d_ident, float eps, const float* d_gain1, void* d_next1,
+                                 const float* d_gain2, void* d_next2, int elem, pa_stream_t stream) {
+    PA_CHECK_ARG(d_x && rows >= 0 && width > 0 && (!d_routed || top > 0) && (!d_next1 || d_gain1) && (!d_next2 || d_gain2));
+    PA_CHECK_ARG(!d_sel_id || (d_routed && d_ident && experts >= 0));
+    if (rows == 0) return PA_OK;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 48 * 1024) return PA_ERR_UNSUPPORTED;
+    PA_DISPATCH_ELEM(elem, residual_add_norm2_kernel<T><<<(unsigned)rows, 256, smem, as_stream(stream)>>>(
+                               d_x, width, static_cast<const T*>(d_y), static_cast<const T*>(d_y2), d_routed, d_sel_w,
+                               d_sel_id, top, experts, static_cast<const T*>(d_ident), eps, d_gain1,
+                               static_cast<T*>(d_next1), d_gain2, static_cast<T*>(d_next2)));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_poly_norm(const void* d_z, int64_t rows, int ff, const float* d_coef, float eps, void* d_out, int elem,
+                        pa_stream_t stream) {
+    PA_CHECK_ARG(d_z && d_coef && d_out && rows >= 0 && ff > 0);
+    if (rows == 0) return PA_OK;
+    PA_DISPATCH_ELEM(elem, poly_norm_kernel<T><<<(unsigned)rows, 256, 0, as_stream(stream)>>>(
+                               static_cast<const T*>(d_z), ff, d_coef, eps, static_cast<T*>(d_out)));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_logit_softcap(float* d_logits, int64_t n, float scale, float cap, pa_stream_t stream) {
+    PA_CHECK_ARG(d_logits && n >= 0 && cap >= 0.f);
+    if (n == 0) return PA_OK;
+    logit_softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(d_logits, n, scale, cap);
     PA_RETURN_LAUNCH_STATUS();
 }
 

@@ -161,6 +161,16 @@ _SIGS = {
     "pa_decay_scan": ([_vp, _i64, _i32, _vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _i64, _i32,
                        _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _sz, _i32, _vp], _i32),
     "pa_gated_rms_norm": ([_vp, _i64, _i32, _i32, _vp, _i64, _i32, _i32, _vp, _f32, _vp, _i32, _vp], _i32),
+    # sink / temperature / kept first positions / turned values; two-norm parallel wiring; polynomial activation
+    "pa_masked_attention_sink": ([_vp, _i64, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _i32,
+                                  _f32, _f32, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp], _i32),
+    "pa_residual_add_norm2": ([_vp, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _f32, _vp, _vp, _vp, _vp, _i32,
+                               _vp], _i32),
+    "pa_poly_norm": ([_vp, _i64, _i32, _vp, _f32, _vp, _i32, _vp], _i32),
+    "pa_logit_softcap": ([_vp, _i64, _f32, _f32, _vp], _i32),
+    "pa_router_topk_biased": ([_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _i32,
+                               _vp], _i32),
+    "pa_causal_conv": ([_vp, _i64, _i32, _i32, _i32, _vp, _vp, _i32, _vp, _vp, _i32, _vp, _i64, _i32, _vp], _i32),
 }
 
 EXPORTS = tuple(_SIGS)

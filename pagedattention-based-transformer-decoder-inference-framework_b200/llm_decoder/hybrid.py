@@ -1,7 +1,7 @@
 """HybridDecoder -- a config-driven decoder stack over a ragged batch: every layer is one MIXER (picked by the layer's
 `type` from MIXERS) plus an optional FEED-FORWARD (picked by `mlp.kind` from FEED_FORWARDS); the residual stream is
 float.  A DESIGN (config "architecture", table DESIGNS) fixes how a layer is wired and with which constants the
-mechanisms are built.  Three designs are served.
+mechanisms are built.  Four designs are served.
 
 `Megusun` (wiring 'parallel': mixer and feed-forward both read the same pre-norm output):
 
@@ -51,6 +51,20 @@ mechanisms are built.  Three designs are served.
   ff 'moe'           softmax router over all experts, experts in groups of neighbours of which only the best `keep`
                      groups (by their largest score) can be chosen, the `top` largest scores un-renormalised on the
                      experts' OUTPUT, silu-gated experts, plus an always-on shared expert
+
+`Gunulorn` (wiring 'parallel_two_norms': x += mixer(N(x; w1)) + ff(N(x; w2)), N(x; w) = x / sqrt(mean(x^2) + eps) * w, both
+  sublayers read the same x); logits = cap * tanh(s * head . N(x; w_final) / cap) with s = logit_scale, cap = logit_softcap:
+
+  mixer 'attention'  causal softmax attention with grouped key/value heads, no biases, no rotation; q, k and v pass a short
+                     causal convolution over time right after their projections (its last taps - 1 inputs are state);
+                     scores (q . k) * scale * temp[h]; a learned sink logit per head joins the softmax denominator; a layer
+                     with `kv_from: j` has only a query projection and reads layer j's pool
+  mixer 'attention_2'  a sliding window that also keeps the sequence's first mask.keep_first positions; interleaved-pair
+                     rotation of the first rot.dims dimensions of q and k; values cached turned by their own position over
+                     all of vdim and each head's output turned back by the query's position; one added to the denominator
+  ff 'dense'         W_down P(W_up h + b_up) + b_down, P(z) = a N(z) + b N(z^2) + c N(z^3) + e (N over the token's ff values)
+  ff 'moe'           softmax router over experts + identity outputs, the `top` largest of score + correction, weights = the
+                     chosen scores over their sum, on the OUTPUT of silu-gated experts; an identity output returns h itself
 
 Every size and constant comes from config.json (or a tensor's shape); the constants a design fixes are the arguments
 the mechanisms are constructed with.  Two precisions: 'bfloat16' (matrix products and their activations in bfloat16
@@ -344,14 +358,28 @@ def log_distance_bucket(n, buckets, far):
 
 
 class MaskedAttention:
-    """Softmax attention with grouped key/value heads and biased projections over a paged pool of its own; the design
-    picks the visibility rule (`mask`: 'causal', 'window' or 'chunk' of cfg mask.size), the distance bias (`bias`: None,
-    'slope' -- minus 2^(-slope_exp (h + 1) / heads) per step of distance -- or 'bucket' -- a learned table '<prefix>rel'
-    [buckets, heads] over log_distance_bucket(distance, buckets, cfg bias_max)) and whether cfg 'softcap' caps the
-    scores.  It reads its q | k | v from a projection buffer at a column offset, so a mixer can fuse its input product
-    with others."""
+    """Softmax attention with grouped key/value heads over a paged pool of its own; the design picks the visibility rule
+    (`mask`: 'causal', 'window' or 'chunk' of cfg mask.size; a window also keeps the first cfg mask.keep_first positions),
+    the distance bias (`bias`: None, 'slope' -- minus 2^(-slope_exp (h + 1) / heads) per step of distance -- or 'bucket' --
+    a learned table '<prefix>rel' [buckets, heads] over log_distance_bucket(distance, buckets, cfg bias_max)), whether cfg
+    'softcap' caps the scores, and
 
-    def __init__(self, model, prefix, cfg, W, mask="causal", bias=None, softcap=False, slope_exp=8.0):
+      proj_bias    whether the four projections have biases ('<name>.b')
+      conv         a short causal convolution (cfg 'conv' taps, weights '<name>.conv' [channels, taps], no bias, no
+                   activation) on q, k and v right after the projection; the last taps - 1 projected rows are state
+      rot          interleaved-pair rotation of the first cfg rot.dims dimensions of every q and k head (cfg rot.base)
+      rot_values   values cached turned by their own position over all of vdim (same pairs, angles p * base^(-2m / vdim));
+                   every head's output is turned back by the query's position inside the attention kernels
+      head_temp    a learned factor per query head on the scaled dot products ('<prefix>temp')
+      sink         'learned': a logit per head ('<prefix>sink') in the softmax denominator, without key or value;
+                   'zero': the same with logit 0 (one added to the denominator)
+
+    A layer whose cfg has `kv_from: j` owns no key / value projections (nor their convolutions): it reads the pool of
+    layer j (keys and values as cached there) with its own queries.  The mixer reads its q | k | v from a projection
+    buffer at a column offset, so a mixer can fuse its input product with others."""
+
+    def __init__(self, model, prefix, cfg, W, mask="causal", bias=None, softcap=False, slope_exp=8.0, proj_bias=True,
+                 conv=False, rot=False, rot_values=False, head_temp=False, sink=None):
         self.heads, self.kv_heads = int(cfg["heads"]), int(cfg["kv_heads"])
         self.dim, self.vdim = int(cfg["dim"]), int(cfg["vdim"])
         if self.heads % self.kv_heads:
@@ -360,18 +388,64 @@ class MaskedAttention:
         self.softcap = float(cfg["softcap"]) if softcap else 0.0
         self.mask_kind = MASK_KIND[mask]
         self.mask_size = int(cfg["mask"]["size"]) if mask != "causal" else 0
+        self.mask_keep = int(cfg["mask"].get("keep_first", 0)) if mask == "window" else 0
+        self.kv_from = cfg.get("kv_from")
+        self.own_kv = self.kv_from is None
         H = self.heads
-        shapes = (("q", H * self.dim), ("k", self.kv_heads * self.dim), ("v", self.kv_heads * self.vdim))
+        shapes = (("q", H * self.dim),) + ((("k", self.kv_heads * self.dim), ("v", self.kv_heads * self.vdim)) if self.own_kv else ())
         for name, rows in shapes:
-            if tuple(W[prefix + name].shape) != (rows, model.width) or tuple(W[prefix + name + ".b"].shape) != (rows,):
+            if tuple(W[prefix + name].shape) != (rows, model.width) or (proj_bias and tuple(W[prefix + name + ".b"].shape) != (rows,)):
                 raise ValueError(f"{prefix}{name}: shape does not match the config")
         if tuple(W[prefix + "o"].shape) != (model.width, H * self.vdim):
             raise ValueError(f"{prefix}o: shape does not match the config")
         self.in_weight = torch.cat([W[prefix + n] for n, _ in shapes], 0)
-        self.in_bias = torch.cat([W[prefix + n + ".b"] for n, _ in shapes], 0)
+        self.in_bias = torch.cat([W[prefix + n + ".b"] for n, _ in shapes], 0) if proj_bias else None
         self.q_cols, self.k_cols = H * self.dim, self.kv_heads * self.dim
-        self.in_cols = self.q_cols + self.k_cols + self.kv_heads * self.vdim
-        self.w_o, self.b_o = model._weight(W[prefix + "o"]), model._bias(W[prefix + "o.b"])
+        self.in_cols = int(self.in_weight.shape[0])
+        self.w_o, self.b_o = model._weight(W[prefix + "o"]), model._bias(W[prefix + "o.b"]) if proj_bias else None
+        self.taps, self.conv_w = 0, None
+        if conv:
+            self.taps = int(cfg["conv"])
+            if not 1 <= self.taps <= 8:
+                raise ValueError(f"{prefix}: 1 to 8 convolution taps are served")
+            for name, rows in shapes:
+                if tuple(W[prefix + name + ".conv"].shape) != (rows, self.taps):
+                    raise ValueError(f"{prefix}{name}.conv: shape does not match the config")
+            self.conv_w = model._f32(torch.cat([W[prefix + n + ".conv"] for n, _ in shapes], 0))
+        self.rot_dims, self.rot_base, self.rot_values = 0, 0.0, bool(rot_values)
+        if rot or rot_values:
+            self.rot_base = float(cfg["rot"]["base"])
+        if rot:
+            self.rot_dims = int(cfg["rot"]["dims"])
+            if self.rot_dims % 2 or self.rot_dims > self.dim:
+                raise ValueError(f"{prefix}: rot.dims must be even and at most dim")
+        if self.rot_values and self.vdim % 2:
+            raise ValueError(f"{prefix}: turned values need an even vdim")
+        self.head_scale = None
+        if head_temp:
+            if tuple(W[prefix + "temp"].shape) != (H,):
+                raise ValueError(f"{prefix}temp: one number per head expected")
+            self.head_scale = model._f32(W[prefix + "temp"])
+        self.sink = None
+        if sink == "learned":
+            if tuple(W[prefix + "sink"].shape) != (H,):
+                raise ValueError(f"{prefix}sink: one number per head expected")
+            self.sink = model._f32(W[prefix + "sink"])
+        elif sink == "zero":
+            self.sink = model._f32(torch.zeros(H))
+        elif sink is not None:
+            raise ValueError(f"unknown sink {sink!r}")
+        self._src = None
+        if not self.own_kv:
+            j = int(self.kv_from)
+            src = model.layers[j].mixer if 0 <= j < len(model.layers) else None
+            src = getattr(src, "core", None)
+            if not isinstance(src, MaskedAttention) or not src.own_kv:
+                raise ValueError(f"{prefix}: kv_from must name an earlier attention layer with a pool of its own")
+            mine = (self.kv_heads, self.dim, self.vdim, self.rot_dims, self.rot_base, self.rot_values)
+            if (src.kv_heads, src.dim, src.vdim, src.rot_dims, src.rot_base, src.rot_values) != mine:
+                raise ValueError(f"{prefix}: key/value heads, sizes and rotation must equal those of layer {j}")
+            self._src = src
         self.bias_kind, self.bias_len, self.bias = 0, 0, None
         if bias == "slope":
             self.bias_kind = 1
@@ -394,47 +468,72 @@ class MaskedAttention:
         self.alloc_state(model)
 
     def alloc_state(self, model):
-        self.kv = model.states.add_kv_layer(self.kv_heads, self.dim, self.vdim, _KV[model.act_dtype])
+        if self.own_kv:
+            self.kv = model.states.add_kv_layer(self.kv_heads, self.dim, self.vdim, _KV[model.act_dtype])
+        else:
+            if getattr(self, "kv", None) is not None:
+                raise ValueError("a layer that borrows keys and values cannot run in a looped block")
+            self.kv = self._src.kv
+        self.conv_state = model.states.add_state((self.taps - 1) * self.in_cols) if self.taps > 1 else None
+
+    def _prepare(self, c, proj, off):
+        """Convolution and rotation of this step's q | k | v rows, then the new keys and values go to the pool.  Returns
+        the buffer and column offset the attention kernels read the queries from."""
+        b, lib, s, R = c.batch, c.lib, _cabi.stream(), c.R
+        if self.taps:
+            chunks, nch, _s0, _sn = b.chunk_items(CONV_CHUNK)
+            y = c.empty(R, self.in_cols)
+            _chk(lib.pa_causal_conv(proj.data_ptr(), proj.stride(0), off, self.in_cols, self.taps, self.conv_w.data_ptr(),
+                                    None, 0, _cabi.ptr(self.conv_state), chunks.data_ptr(), nch, y.data_ptr(), self.in_cols,
+                                    c.elem, s), "pa_causal_conv")
+            if self.taps > 1:
+                _chk(lib.pa_conv_state_update(proj.data_ptr(), proj.stride(0), off, self.in_cols, self.taps,
+                                              b.seq_start.data_ptr(), b.seq_len.data_ptr(), b.seq_slot.data_ptr(),
+                                              b.num_seqs, self.conv_state.data_ptr(), c.elem, s), "pa_conv_state_update")
+            proj, off = y, 0
+        k_off, v_off = off + self.q_cols, off + self.q_cols + self.k_cols
+        if self.rot_dims:
+            rope = c.rope_table(self.rot_dims, self.rot_base)
+            for col, heads in ((off, self.heads),) + (((k_off, self.kv_heads),) if self.own_kv else ()):
+                _chk(lib.pa_rope_rows(proj.data_ptr(), proj.stride(0), col, self.dim, heads, self.rot_dims, rope.data_ptr(), R,
+                                      c.elem, s), "pa_rope_rows")
+        if self.own_kv:
+            if self.rot_values:
+                _chk(lib.pa_rope_rows(proj.data_ptr(), proj.stride(0), v_off, self.vdim, self.kv_heads, self.vdim,
+                                      c.rope_table(self.vdim, self.rot_base).data_ptr(), R, c.elem, s), "pa_rope_rows")
+            self.kv.append_rows(proj, k_off, v_off, b.row_slot, b.row_pos)
+        return proj, off
 
     def attend(self, c, proj, off):
         """proj [R, stride] holds q | k | v of this step's rows from column `off`; appends k / v to the pool and
         returns the heads' outputs [R, heads * vdim]."""
-        b, lib, kv, s = c.batch, c.lib, self.kv, _cabi.stream()
-        kv.append_rows(proj, off + self.q_cols, off + self.q_cols + self.k_cols, b.row_slot, b.row_pos)
+        proj, off = self._prepare(c, proj, off)
         out = c.empty(c.R, self.heads * self.vdim)
-        pt = kv.page_table_
-        table = pt.device_data()
-        for kind, group in b.query_tiles(self.tile_tokens, self.mma_tokens, MMA_FROM).items():
-            if group is None:
-                continue
-            tiles, ntiles, _longest = group
-            st = lib.pa_masked_attention(proj.data_ptr(), proj.stride(0), off, kv.key_buffer_.data_ptr(),
-                                         kv.value_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_, pt.num_heads_,
-                                         pt.num_tiles_, kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles,
-                                         self.heads, self.dim, self.vdim, self.scale, self.softcap, self.mask_kind,
-                                         self.mask_size, self.bias_kind, _cabi.ptr(self.bias), self.bias_len,
-                                         out.data_ptr(), c.elem, kind, s)
-            if kind == 2 and st == _cabi.PA_ERR_UNSUPPORTED:    # a stride or an alignment the tensor-core kernel refuses
-                self.mma_tokens = 0
-                return self.attend_tiles_float(c, proj, off, out)
-            _chk(st, "pa_masked_attention")
+        if not self._attend_tiles(c, proj, off, out, self.mma_tokens):
+            self.mma_tokens = 0     # a stride or an alignment the tensor-core kernel refuses: the float kernels
+            self._attend_tiles(c, proj, off, out, 0)
         return out
 
-    def attend_tiles_float(self, c, proj, off, out):
+    def _attend_tiles(self, c, proj, off, out, mma_tokens):
         b, lib, kv, s = c.batch, c.lib, self.kv, _cabi.stream()
         pt = kv.page_table_
         table = pt.device_data()
-        for kind, group in b.query_tiles(self.tile_tokens, 0, MMA_FROM).items():
+        out_rot = c.rope_table(self.vdim, self.rot_base) if self.rot_values else None
+        for kind, group in b.query_tiles(self.tile_tokens, mma_tokens, MMA_FROM).items():
             if group is None:
                 continue
             tiles, ntiles, _longest = group
-            _chk(lib.pa_masked_attention(proj.data_ptr(), proj.stride(0), off, kv.key_buffer_.data_ptr(),
-                                         kv.value_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_, pt.num_heads_,
-                                         pt.num_tiles_, kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles,
-                                         self.heads, self.dim, self.vdim, self.scale, self.softcap, self.mask_kind,
-                                         self.mask_size, self.bias_kind, _cabi.ptr(self.bias), self.bias_len,
-                                         out.data_ptr(), c.elem, kind, s), "pa_masked_attention")
-        return out
+            st = lib.pa_masked_attention_sink(proj.data_ptr(), proj.stride(0), off, kv.key_buffer_.data_ptr(),
+                                              kv.value_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_, pt.num_heads_,
+                                              pt.num_tiles_, kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles,
+                                              self.heads, self.dim, self.vdim, self.scale, self.softcap, self.mask_kind,
+                                              self.mask_size, self.mask_keep, self.bias_kind, _cabi.ptr(self.bias),
+                                              self.bias_len, _cabi.ptr(self.head_scale), _cabi.ptr(self.sink),
+                                              _cabi.ptr(out_rot), out.data_ptr(), c.elem, kind, s)
+            if kind == 2 and st == _cabi.PA_ERR_UNSUPPORTED:
+                return False
+            _chk(st, "pa_masked_attention_sink")
+        return True
 
     def project_out(self, c, heads_out):
         return c.model._linear(heads_out, self.w_o, bias=self.b_o)
@@ -611,26 +710,43 @@ _EXPERT_ACT = {"silu": 0, "relu": 1, "relu2": 2}
 
 
 class DenseFF:
-    """W_down act(W_up h) (gated=False, act 'gelu_erf'), or the gated form W_down (act(W_gate h) * (W_up h))."""
+    """W_down act(W_up h) (gated=False; act 'gelu_erf', or 'poly_norm': a N(z) + b N(z^2) + c N(z^3) + e with the four
+    numbers of '<prefix>act', N = division by the root mean square over the token's ff values), or the gated form
+    W_down (act(W_gate h) * (W_up h)).  bias=True: both products have biases ('<name>.b')."""
     kind = "dense"
 
-    def __init__(self, model, prefix, cfg, W, act="gelu_erf", gated=False):
+    def __init__(self, model, prefix, cfg, W, act="gelu_erf", gated=False, bias=False):
         self.gated, self.act = bool(gated), act
-        if (self.gated and act not in _GLU_ACT) or (not self.gated and act != "gelu_erf"):
+        if (self.gated and act not in _GLU_ACT) or (not self.gated and act not in ("gelu_erf", "poly_norm")):
             raise ValueError(f"dense feed-forward: activation {act!r} is not served")
         self.ff = int(W[prefix + "up"].shape[0])
+        if "ff" in cfg and int(cfg["ff"]) != self.ff:
+            raise ValueError(f"{prefix}up: shape does not match the config")
         self.w_up = model._weight(torch.cat([W[prefix + "gate"], W[prefix + "up"]], 0) if self.gated else W[prefix + "up"])
         self.w_down = model._weight(W[prefix + "down"])
+        self.b_up = self.b_down = self.coef = None
+        if bias:
+            names = ("gate.b", "up.b") if self.gated else ("up.b",)
+            self.b_up = model._bias(torch.cat([W[prefix + n] for n in names], 0))
+            self.b_down = model._bias(W[prefix + "down.b"])
+        if act == "poly_norm":
+            if tuple(W[prefix + "act"].shape) != (4,):
+                raise ValueError(f"{prefix}act: four numbers expected")
+            self.coef = model._f32(W[prefix + "act"])
 
     def forward(self, c, h):
-        a = c.model._linear(h, self.w_up)
+        a = c.model._linear(h, self.w_up, bias=self.b_up)
         if self.gated:
             gu, a = a, c.empty(c.R, self.ff)
             _chk(c.lib.pa_act_mul(gu.data_ptr(), c.R, self.ff, _GLU_ACT[self.act], a.data_ptr(), c.elem, _cabi.stream()),
                  "pa_act_mul")
+        elif self.act == "poly_norm":
+            z, a = a, c.empty(c.R, self.ff)
+            _chk(c.lib.pa_poly_norm(z.data_ptr(), c.R, self.ff, self.coef.data_ptr(), c.model.eps, a.data_ptr(), c.elem,
+                                    _cabi.stream()), "pa_poly_norm")
         else:
             _chk(c.lib.pa_gelu_inplace(a.data_ptr(), a.numel(), c.elem, _cabi.stream()), "pa_gelu_inplace")
-        return dict(dense=c.model._linear(a, self.w_down))
+        return dict(dense=c.model._linear(a, self.w_down, bias=self.b_down))
 
 
 _SCORE_FN = {"sigmoid": 0, "softmax": 1, "softmax_chosen": 2}
@@ -643,19 +759,35 @@ class MoEFF:
     the expert's input row; 'output': the weighted sum of the experts' outputs), gated experts W_down(act(W_gate a) *
     W_up a) or plain ones W_down act(W_up a), and an optional shared expert (gated per token where '<prefix>shared.sg'
     exists).  cfg router.groups {count, keep}: experts in `count` equal groups of neighbours, only the `keep` groups with
-    the largest maxima can be chosen."""
+    the largest maxima can be chosen.  correction=True: '<prefix>correction' (one number per router output) is added to
+    the scores for the CHOICE only; renorm=True: the chosen scores are divided by their sum.  cfg router.identity = n: the
+    router has n more outputs than there are experts, and a token that chooses one of those gets its own input row back
+    from it (weight_on 'output'); such experts have no tensors."""
     kind = "moe"
 
-    def __init__(self, model, prefix, cfg, W, score="sigmoid", weight_on="input", act="silu", gated=True):
+    def __init__(self, model, prefix, cfg, W, score="sigmoid", weight_on="input", act="silu", gated=True, correction=False,
+                 renorm=False):
         self.experts, self.top = int(cfg["router"]["experts"]), int(cfg["router"]["top"])
+        self.identity = int(cfg["router"].get("identity", 0))
+        self.outputs = self.experts + self.identity
         self.ff = int(cfg["expert"]["ff"])
         grp = cfg["router"].get("groups") or {}
         self.ngroups, self.keep = int(grp.get("count", 1)), int(grp.get("keep", grp.get("count", 1)))
-        if self.experts % self.ngroups or not 1 <= self.keep <= self.ngroups or self.keep * (self.experts // self.ngroups) < self.top:
+        if self.outputs % self.ngroups or not 1 <= self.keep <= self.ngroups or self.keep * (self.outputs // self.ngroups) < self.top:
             raise ValueError("routed feed-forward: expert groups do not fit experts / top")
         self.score_fn, self.weight_on, self.act, self.gated = _SCORE_FN[score], weight_on, _EXPERT_ACT[act], bool(gated)
-        if weight_on not in ("input", "output") or not 0 < self.top <= self.experts:
+        self.renorm = 1 if renorm else 0
+        if weight_on not in ("input", "output") or not 0 < self.top <= self.outputs or self.identity < 0:
             raise ValueError("routed feed-forward: bad constants")
+        if self.identity and weight_on != "output":
+            raise ValueError("routed feed-forward: identity experts need the weight on the output")
+        if tuple(W[prefix + "router"].shape) != (self.outputs, model.width):
+            raise ValueError(f"{prefix}router: shape does not match experts + identity")
+        self.choice_bias = None
+        if correction:
+            if tuple(W[prefix + "correction"].shape) != (self.outputs,):
+                raise ValueError(f"{prefix}correction: one number per router output expected")
+            self.choice_bias = model._f32(W[prefix + "correction"])
         ex = lambda n: [W[f"{prefix}e{e}.{n}"] for e in range(self.experts)]  # noqa: E731
         if self.gated:
             self.w_gate_up = model._weight_raw(torch.stack([torch.cat([g, u], 0) for g, u in zip(ex("gate"), ex("up"))]))
@@ -678,10 +810,11 @@ class MoEFF:
         sel_id, sel_w = c.empty(pairs, **i32), c.empty(pairs, **f32)
         sh = self.shared
         sgate = c.empty(R, **f32) if sh and sh["w_sg"] is not None else None
-        _chk(lib.pa_router_topk_grouped(h.data_ptr(), self.w_router.data_ptr(), _cabi.ptr(self.b_router),
-                                        _cabi.ptr(sh["w_sg"]) if sgate is not None else None, R, wdt, self.experts,
-                                        self.top, self.score_fn, 0, self.ngroups, self.keep, sel_id.data_ptr(),
-                                        sel_w.data_ptr(), _cabi.ptr(sgate), c.elem, s), "pa_router_topk_grouped")
+        _chk(lib.pa_router_topk_biased(h.data_ptr(), self.w_router.data_ptr(), _cabi.ptr(self.b_router),
+                                       _cabi.ptr(sh["w_sg"]) if sgate is not None else None, R, wdt, self.outputs,
+                                       self.top, self.score_fn, self.renorm, self.ngroups, self.keep,
+                                       _cabi.ptr(self.choice_bias), sel_id.data_ptr(), sel_w.data_ptr(), _cabi.ptr(sgate),
+                                       c.elem, s), "pa_router_topk_biased")
         order = c.empty(pairs, **i32)
         meta = c.empty(lib.pa_moe_meta_ints(pairs, self.experts), **i32)
         _chk(lib.pa_moe_sort(sel_id.data_ptr(), pairs, self.experts, order.data_ptr(), meta.data_ptr(), s), "pa_moe_sort")
@@ -694,6 +827,8 @@ class MoEFF:
         _chk(lib.pa_moe_down(act.data_ptr(), self.w_down.data_ptr(), self.ff, wdt, self.experts, order.data_ptr(),
                              meta.data_ptr(), pairs, routed.data_ptr(), c.elem, s), "pa_moe_down")
         out = dict(routed=routed, top=self.top, sel_w=sel_w if self.weight_on == "output" else None)
+        if self.identity:       # ids from `experts` on were left out by the sort: the residual kernel reads h for them
+            out.update(sel_id=sel_id, experts=self.experts, ident=h)
         if sh:
             gu = c.model._linear(h, sh["w_gate_up"])
             a = c.empty(R, sh["ff"])
@@ -716,6 +851,14 @@ DESIGNS = {
                             "parallel": (ParallelMixer, dict(left=dict(mask="chunk", bias="slope", slope_exp=8.0))),
                             "mamba2": (Mamba2Mixer, {})},
                     ff={"moe": dict(score="softmax", weight_on="output", act="silu", gated=True)}),
+    "Gunulorn": dict(wiring="parallel_two_norms",
+                     mixers={"attention": (SoftmaxAttentionMixer, dict(mask="causal", proj_bias=False, conv=True,
+                                                                       head_temp=True, sink="learned")),
+                             "attention_2": (SoftmaxAttentionMixer, dict(mask="window", proj_bias=False, rot=True,
+                                                                         rot_values=True, sink="zero"))},
+                     ff={"dense": dict(act="poly_norm", gated=False, bias=True),
+                         "moe": dict(score="softmax", weight_on="output", act="silu", gated=True, correction=True,
+                                     renorm=True)}),
 }
 
 
@@ -746,15 +889,19 @@ class HybridDecoder:
             raise ValueError("embed does not match config vocab / width")
         self.embed = W["embed"].to(self.device, self.act_dtype).contiguous()
         self.head = self._weight(W["head"])
-        post, pre = self.wiring == "post_norm", self.wiring == "pre_norm"
-        self.final_gain = 1.0 if post or pre else float(W["final.norm"].to(torch.float32))
-        self.final_gain_vec = self._f32(W["final.norm"].reshape(-1)) if post else self._gain1p(W["final.norm"]) if pre else None
+        post, pre, par2 = self.wiring == "post_norm", self.wiring == "pre_norm", self.wiring == "parallel_two_norms"
+        self.final_gain = 1.0 if post or pre or par2 else float(W["final.norm"].to(torch.float32))
+        self.final_gain_vec = (self._f32(W["final.norm"].reshape(-1)) if post or par2 else
+                               self._gain1p(W["final.norm"]) if pre else None)
+        if self.final_gain_vec is not None and self.final_gain_vec.numel() != self.width:
+            raise ValueError("final.norm does not match width")
+        self.logit_scale, self.logit_softcap = float(config.get("logit_scale", 1.0)), float(config.get("logit_softcap", 0.0))
         mixers = self.design.get("mixers") or {k: (v, {}) for k, v in MIXERS.items()}
         self.layers = []
         for i, lc in enumerate(config["layers"]):
             L = _Layer()
             p = f"l{i}."
-            if post:    # per-channel gains of the norms on the two sublayers' outputs
+            if post or par2:    # per-channel gains: post-norm on the two sublayers' outputs; two norms of the same x in front of them
                 L.gain1 = self._f32(W[p + "norm1"].reshape(-1))
                 L.gain2 = self._f32(W[p + "norm2"].reshape(-1)) if lc.get("mlp") else None
                 L.shift = L.prev = None
@@ -824,7 +971,7 @@ class HybridDecoder:
 
     def _bias(self, t):
         """A linear layer's bias for _linear: the activation type for the vendor GEMM's epilogue, float for the fp32 kernel."""
-        return t.to(self.act_dtype).to(self.device).contiguous()
+        return None if t is None else t.to(self.act_dtype).to(self.device).contiguous()
 
     def _weight_raw(self, t):
         """[.., out, in] in the activation type (the grouped kernels read the stored orientation)."""
@@ -869,6 +1016,8 @@ class HybridDecoder:
             self._post_norm_layers(c, x)
         elif self.wiring == "pre_norm":
             x = self._pre_norm_layers(c, x)
+        elif self.wiring == "parallel_two_norms":
+            self._parallel_two_norm_layers(c, x)
         for L in self.layers if self.wiring == "parallel" else ():
             h = c.empty(R, W)
             hs = c.empty(R, W) if L.shift is not None else None
@@ -897,7 +1046,41 @@ class HybridDecoder:
         hf = torch.empty((n, W), dtype=self.act_dtype, device=self.device)
         _chk(lib.pa_rms_norm_shift(xs.data_ptr(), n, W, self.eps, self.final_gain, _cabi.ptr(self.final_gain_vec), None, None,
                                    None, None, hf.data_ptr(), None, c.elem, s), "pa_rms_norm_shift")
-        return self._linear(hf, self.head, out_dtype=torch.float32)
+        logits = self._linear(hf, self.head, out_dtype=torch.float32)
+        if self.logit_scale != 1.0 or self.logit_softcap > 0.0:
+            _chk(lib.pa_logit_softcap(logits.data_ptr(), logits.numel(), self.logit_scale, self.logit_softcap, s),
+                 "pa_logit_softcap")
+        return logits
+
+    def _parallel_two_norm_layers(self, c, x):
+        """x += mixer(N(x; w1)) + ff(N(x; w2)): both sublayers read the same x through norms that differ only in their
+        gains.  pa_residual_add_norm2 adds a layer's outputs to the float residual and leaves BOTH operands of the next
+        layer (one mean square) in the activation type."""
+        lib, R, W, s = self._lib, c.R, self.width, _cabi.stream()
+
+        def add_norm(add, nxt):
+            if add.get("shared") is not None:
+                raise ValueError("a shared expert is not served in the two-norm parallel wiring")
+            h1 = c.empty(R, W) if nxt is not None else None
+            h2 = c.empty(R, W) if nxt is not None and nxt.gain2 is not None else None
+            _chk(lib.pa_residual_add_norm2(x.data_ptr(), R, W, _cabi.ptr(add.get("y")), _cabi.ptr(add.get("dense")),
+                                           _cabi.ptr(add.get("routed")), _cabi.ptr(add.get("sel_w")),
+                                           _cabi.ptr(add.get("sel_id")), add.get("top", 0), add.get("experts", 0),
+                                           _cabi.ptr(add.get("ident")), self.eps,
+                                           _cabi.ptr(nxt.gain1) if nxt is not None else None, _cabi.ptr(h1),
+                                           _cabi.ptr(nxt.gain2) if h2 is not None else None, _cabi.ptr(h2), c.elem, s),
+                 "pa_residual_add_norm2")
+            return h1, h2
+
+        layers = self.layers
+        h1, h2 = add_norm({}, layers[0]) if layers else (None, None)
+        for i, L in enumerate(layers):
+            add = dict(y=L.mixer.forward(c, h1))
+            if L.ff is not None:
+                add.update(L.ff.forward(c, h2))
+            h1, h2 = add_norm(add, layers[i + 1] if i + 1 < len(layers) else None)
+            if self.layer_hook is not None:
+                self.layer_hook(x)
 
     def _post_norm_layers(self, c, x):
         """x += N(mixer(x)), then x += N(ff(x)): the sublayers read the residual itself (rounded to the activation type

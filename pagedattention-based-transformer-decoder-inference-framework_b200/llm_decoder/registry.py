@@ -46,7 +46,7 @@ def _fixed_decoder(cls_name):
     return load
 
 
-for _arch in ("Megusun", "Domilix", "Dubarax"):
+for _arch in ("Megusun", "Domilix", "Dubarax", "Gunulorn"):
     register_model(_arch, _load_hybrid)
 register_model("CUDADecoder", _fixed_decoder("CUDADecoder"))
 register_model("INT8Decoder", _fixed_decoder("INT8Decoder"))
