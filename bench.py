@@ -29,6 +29,8 @@ extra  = the other BASELINE.json configurations under the same clock (benchmarks
          wiring) next to the `Megusun` design at equal size, and its kernels against their rooflines.
 --dubarax: likewise (benchmarks/dubarax.py): the stack serving the `Dubarax` design (pre-norm wiring, a looped block,
          windowed / chunked attention, linear attention, a state-space mixer, group-limited experts) next to `Megusun`.
+--gunulorn: likewise (benchmarks/gunulorn.py): the stack serving the `Gunulorn` design (two-norm parallel wiring, attention
+         with convolved projections / sinks / a kept prefix / turned values, PolyNorm, identity experts) next to `Dubarax`.
 N > 1: one process per GPU (torchrun), rows sharded across ranks, no data-path collective in the headline
          step; c5_splitkv is the mode with an exchange.
 """
@@ -74,6 +76,11 @@ def parse():
                          "the Dubarax design (windowed / chunked attention, linear attention, state space, grouped router) at "
                          "realistic layer sizes next to the Megusun design at equal size, and its kernels against their "
                          "rooflines (benchmarks/dubarax.py); one JSON line")
+    ap.add_argument("--gunulorn", action="store_true",
+                    help="instead of the headline workload: prefill / decode throughput of the config-driven stack serving "
+                         "the Gunulorn design at realistic layer sizes next to the Dubarax design at equal size, and its "
+                         "kernels next to the like kernels of that design against their rooflines (benchmarks/gunulorn.py); "
+                         "one JSON line")
     ap.add_argument("--latent", action="store_true",
                     help="instead of the headline workload: prefill / decode throughput of the config-driven stack serving "
                          "the Domilix design (latent attention) at realistic layer sizes next to the Megusun design at "
@@ -459,6 +466,10 @@ def main():
     if args.dubarax:
         from benchmarks import dubarax
         print(json.dumps({"bench": "dubarax", **dubarax.run()}, default=float))
+        return
+    if args.gunulorn:
+        from benchmarks import gunulorn
+        print(json.dumps({"bench": "gunulorn", **gunulorn.run()}, default=float))
         return
     if args.latent:
         from benchmarks import latent

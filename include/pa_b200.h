@@ -736,6 +736,15 @@ int pa_masked_attention(const void* d_q, int64_t q_stride, int q_off, const void
  * d_sink [heads] (NULL: none): exp(d_sink[h]) joins head h's softmax denominator (no key, no value; zeros add one to the
  * denominator); d_out_rot [rows][vdim / 2][cos, sin] (NULL: none; a pa_rope_table over vdim): the neighbouring pairs of
  * every head's output are turned back by the row's angle, in float, before the result is rounded. */
+/* pa_rope_kv_append: the rotation of one step's q | k | v rows and their append in one launch.  Query head h (columns
+ * q_off + h * dim of the row) is rotated in place over its first rot_dims dimensions (neighbouring pairs, d_rope
+ * [rows][rot_dims / 2][cos, sin]); with pools given, the key of kv head g (k_off + g * dim) goes to the row's place in
+ * the pool rotated the same way and its value (v_off + g * vdim) turned over all of vdim by d_value_rope
+ * [rows][vdim / 2][cos, sin] (NULL: as it is).  d_k_pool NULL: a layer that reads another layer's pool. */
+int pa_rope_kv_append(void* d_src, int64_t src_stride, int q_off, int k_off, int v_off, int heads, int kv_heads, int dim,
+                      int vdim, int rot_dims, const float* d_rope, const float* d_value_rope, void* d_k_pool,
+                      void* d_v_pool, const int32_t* d_table, int num_slots, int num_tiles, int total_pages, int tile_size,
+                      const int32_t* d_row_slot, const int32_t* d_row_pos, int rows, int elem, pa_stream_t stream);
 int pa_masked_attention_sink(const void* d_q, int64_t q_stride, int q_off, const void* d_k_pool, const void* d_v_pool,
                              const int32_t* d_table, int num_slots, int num_kv_heads, int num_tiles, int total_pages,
                              int tile_size, const int32_t* d_q_tiles, int num_q_tiles, int heads, int dim, int vdim,

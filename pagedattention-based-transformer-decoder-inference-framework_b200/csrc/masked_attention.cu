@@ -26,6 +26,57 @@
 
 namespace pa {
 
+// ---- rotation of this step's q | k | v rows fused with the append ----------------------------------------------------
+// One warp per (row, unit): units [0, heads) are the query heads, rotated in place over their first rot_dims dimensions;
+// units [heads, heads + kv_heads) are the key/value heads of a layer with a pool of its own: the key goes to its place in
+// the pool rotated the same way, the value turned over all of vdim (vrot != null) or as it is.  Pairs are neighbours
+// (2m, 2m + 1); the tables hold [rows][dims / 2][cos, sin] of the batch rows.
+template <typename T>
+__device__ __forceinline__ void ma_turn_copy(const T* __restrict__ src, T* __restrict__ dst, int n, int dims,
+                                             const float* __restrict__ t, int lane) {
+    for (int d = 2 * lane; d < n; d += 64) {
+        float u = to_f32<T>(src[d]), v = d + 1 < n ? to_f32<T>(src[d + 1]) : 0.f;
+        if (t && d + 1 < dims) {
+            const float c = t[d], sn = t[d + 1];          // pair d / 2: entries (d / 2) * 2 and + 1
+            const float u0 = u;
+            u = u0 * c - v * sn;
+            v = v * c + u0 * sn;
+        }
+        dst[d] = from_f32<T>(u);
+        if (d + 1 < n) dst[d + 1] = from_f32<T>(v);
+    }
+}
+
+template <typename T>
+__global__ void rope_kv_append_kernel(T* __restrict__ src, int64_t stride, int q_off, int k_off, int v_off, int heads,
+                                      int kv_heads, int dim, int vdim, int rot_dims, const float* __restrict__ rope,
+                                      const float* __restrict__ vrot, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                      const int32_t* __restrict__ table, int num_slots, int num_tiles, int total_pages,
+                                      int tile_size, const int32_t* __restrict__ row_slot,
+                                      const int32_t* __restrict__ row_pos, int rows) {
+    const int lane = threadIdx.x & 31;
+    const int units = heads + (k_pool ? kv_heads : 0);
+    const int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (w >= (int64_t)rows * units) return;
+    const int u = (int)(w % units);
+    const int64_t r = w / units;
+    T* row = src + r * stride;
+    const float* rt = rope ? rope + r * (rot_dims >> 1) * 2 : nullptr;
+    if (u < heads) {
+        if (rt) ma_turn_copy<T>(row + q_off + (int64_t)u * dim, row + q_off + (int64_t)u * dim, rot_dims, rot_dims, rt, lane);
+        return;
+    }
+    const int g = u - heads;
+    const int slot = row_slot[r], pos = row_pos[r];
+    if (pos < 0 || pos / tile_size >= num_tiles || (unsigned)slot >= (unsigned)num_slots) return;
+    const int page = table[((int64_t)slot * kv_heads + g) * num_tiles + pos / tile_size];
+    if (page < 0 || page >= total_pages) return;
+    const int64_t prow = (int64_t)page * tile_size + pos % tile_size;
+    ma_turn_copy<T>(row + k_off + (int64_t)g * dim, k_pool + prow * dim, dim, rot_dims, rt, lane);
+    ma_turn_copy<T>(row + v_off + (int64_t)g * vdim, v_pool + prow * vdim, vdim, vdim,
+                    vrot ? vrot + r * (vdim >> 1) * 2 : nullptr, lane);
+}
+
 constexpr int kMaRows = 32;     // (token, head) rows per CTA
 constexpr int kMaWarps = 8;
 constexpr int kMaRpw = kMaRows / kMaWarps;
@@ -821,6 +872,26 @@ PA_API int pa_masked_attention_sink(const void* d_q, int64_t q_stride, int q_off
     }
     if (elem == 4) return ma_dispatch<float>(p, num_q_tiles, as_stream(stream));
     return ma_dispatch<bf16_t>(p, num_q_tiles, as_stream(stream));
+}
+
+PA_API int pa_rope_kv_append(void* d_src, int64_t src_stride, int q_off, int k_off, int v_off, int heads, int kv_heads,
+                             int dim, int vdim, int rot_dims, const float* d_rope, const float* d_value_rope,
+                             void* d_k_pool, void* d_v_pool, const int32_t* d_table, int num_slots, int num_tiles,
+                             int total_pages, int tile_size, const int32_t* d_row_slot, const int32_t* d_row_pos, int rows,
+                             int elem, pa_stream_t stream) {
+    PA_CHECK_ARG(d_src && rows >= 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0);
+    PA_CHECK_ARG(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dim && (rot_dims == 0 || d_rope));
+    PA_CHECK_ARG(!d_value_rope || vdim % 2 == 0);
+    PA_CHECK_ARG(!d_k_pool || (d_v_pool && d_table && d_row_slot && d_row_pos && num_slots > 0 && num_tiles > 0 &&
+                               total_pages > 0 && tile_size > 0));
+    if (rows == 0) return PA_OK;
+    const int64_t threads = (int64_t)rows * (heads + (d_k_pool ? kv_heads : 0)) * 32;
+    PA_DISPATCH_ELEM(elem, rope_kv_append_kernel<T><<<(unsigned)((threads + 255) / 256), 256, 0, as_stream(stream)>>>(
+                               static_cast<T*>(d_src), src_stride, q_off, k_off, v_off, heads, kv_heads, dim, vdim, rot_dims,
+                               rot_dims ? d_rope : nullptr, d_value_rope, static_cast<T*>(d_k_pool),
+                               static_cast<T*>(d_v_pool), d_table, num_slots, num_tiles, total_pages, tile_size, d_row_slot,
+                               d_row_pos, rows));
+    PA_RETURN_LAUNCH_STATUS();
 }
 
 PA_API int pa_masked_attention_mma_tile_tokens(int dim, int vdim, int elem) {

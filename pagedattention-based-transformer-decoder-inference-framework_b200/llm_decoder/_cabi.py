@@ -164,6 +164,8 @@ _SIGS = {
     # sink / temperature / kept first positions / turned values; two-norm parallel wiring; polynomial activation
     "pa_masked_attention_sink": ([_vp, _i64, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _i32,
                                   _f32, _f32, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp], _i32),
+    "pa_rope_kv_append": ([_vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
+                           _i32, _i32, _vp, _vp, _i32, _i32, _vp], _i32),
     "pa_residual_add_norm2": ([_vp, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _f32, _vp, _vp, _vp, _vp, _i32,
                                _vp], _i32),
     "pa_poly_norm": ([_vp, _i64, _i32, _vp, _f32, _vp, _i32, _vp], _i32),

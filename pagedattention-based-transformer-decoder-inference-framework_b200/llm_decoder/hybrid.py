@@ -492,16 +492,19 @@ class MaskedAttention:
                                               b.num_seqs, self.conv_state.data_ptr(), c.elem, s), "pa_conv_state_update")
             proj, off = y, 0
         k_off, v_off = off + self.q_cols, off + self.q_cols + self.k_cols
-        if self.rot_dims:
-            rope = c.rope_table(self.rot_dims, self.rot_base)
-            for col, heads in ((off, self.heads),) + (((k_off, self.kv_heads),) if self.own_kv else ()):
-                _chk(lib.pa_rope_rows(proj.data_ptr(), proj.stride(0), col, self.dim, heads, self.rot_dims, rope.data_ptr(), R,
-                                      c.elem, s), "pa_rope_rows")
-        if self.own_kv:
-            if self.rot_values:
-                _chk(lib.pa_rope_rows(proj.data_ptr(), proj.stride(0), v_off, self.vdim, self.kv_heads, self.vdim,
-                                      c.rope_table(self.vdim, self.rot_base).data_ptr(), R, c.elem, s), "pa_rope_rows")
-            self.kv.append_rows(proj, k_off, v_off, b.row_slot, b.row_pos)
+        kv = self.kv
+        if self.rot_dims or self.rot_values:    # q in place; k rotated and v turned on their way into the pool: one launch
+            pt = kv.page_table_
+            own = self.own_kv
+            _chk(lib.pa_rope_kv_append(proj.data_ptr(), proj.stride(0), off, k_off, v_off, self.heads, self.kv_heads, self.dim,
+                                       self.vdim, self.rot_dims, _cabi.ptr(c.rope_table(self.rot_dims, self.rot_base)),
+                                       _cabi.ptr(c.rope_table(self.vdim, self.rot_base)) if self.rot_values else None,
+                                       kv.key_buffer_.data_ptr() if own else None,
+                                       kv.value_buffer_.data_ptr() if own else None, pt.device_data().data_ptr(),
+                                       pt.num_beams_, pt.num_tiles_, kv.total_pages_, kv.tile_size_, b.row_slot.data_ptr(),
+                                       b.row_pos.data_ptr(), R, c.elem, s), "pa_rope_kv_append")
+        elif self.own_kv:
+            kv.append_rows(proj, k_off, v_off, b.row_slot, b.row_pos)
         return proj, off
 
     def attend(self, c, proj, off):
