@@ -405,7 +405,9 @@ class MaskedAttention:
         self.w_o, self.b_o = model._weight(W[prefix + "o"]), model._bias(W[prefix + "o.b"]) if proj_bias else None
         self.taps, self.conv_w = 0, None
         if conv:
-            self.taps = int(cfg["conv"])
+            self.taps = int(W[prefix + "q.conv"].shape[-1])     # the tensors' shape gives the taps; cfg 'conv' must agree
+            if int(cfg.get("conv", self.taps)) != self.taps:
+                raise ValueError(f"{prefix}q.conv: shape does not match the config")
             if not 1 <= self.taps <= 8:
                 raise ValueError(f"{prefix}: 1 to 8 convolution taps are served")
             for name, rows in shapes:
@@ -773,7 +775,7 @@ class MoEFF:
         self.experts, self.top = int(cfg["router"]["experts"]), int(cfg["router"]["top"])
         self.identity = int(cfg["router"].get("identity", 0))
         self.outputs = self.experts + self.identity
-        self.ff = int(cfg["expert"]["ff"])
+        self.ff = int((cfg.get("expert") or {}).get("ff", W[prefix + "e0.up"].shape[0] if self.experts else 0))
         grp = cfg["router"].get("groups") or {}
         self.ngroups, self.keep = int(grp.get("count", 1)), int(grp.get("keep", grp.get("count", 1)))
         if self.outputs % self.ngroups or not 1 <= self.keep <= self.ngroups or self.keep * (self.outputs // self.ngroups) < self.top:

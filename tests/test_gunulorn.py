@@ -799,6 +799,20 @@ def test_configuration_errors():
     bad["layers"][0]["mlp"]["router"]["identity"] = 1       # the router has other rows
     with pytest.raises(ValueError):
         _model(bad, W)
+    config, W = _case("conv")
+    bad = json.loads(json.dumps(config))
+    bad["layers"][0]["mixer"]["conv"] += 1                  # taps unlike the tensors'
+    with pytest.raises(ValueError):
+        _model(bad, W)
+    bare = json.loads(json.dumps(config))
+    del bare["layers"][0]["mixer"]["conv"]                  # the tensors' shape alone gives the taps
+    toks = _tokens(20, config["vocab"], 5)
+    _close(ld_step(_model(bare, W), toks), _oracle("conv0", config, W, toks))
+
+
+def ld_step(model, tokens):
+    import llm_decoder as ld
+    return ld.Engine(model).step([("a", tokens, list(range(len(tokens))))])
 
 
 # ---- the command-line programs -------------------------------------------------------------------------------------------
