@@ -1,6 +1,6 @@
 #!/usr/bin/env python
 """C3: beam width 4 with shared-prefix pages, 32 groups (128 rows), 2K ctx = 1792 shared + 256
-private tokens per beam (BASELINE.json configs[2]; SURVEY 8d).  Reports achieved GB/s on UNIQUE
+private tokens per beam (BASELINE.json configs[2]).  Reports achieved GB/s on UNIQUE
 bytes (the algorithmic figure) and on logical bytes for each kernel."""
 import argparse
 import json

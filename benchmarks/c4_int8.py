@@ -1,6 +1,6 @@
 #!/usr/bin/env python
 """C4: INT8 KV cache + INT8 MLP GEMMs, Llama-7B shape (32 heads, D=128, hidden 4096, MLP 4x), batch
-256 decode rows in total sharded over N GPUs (BASELINE.json configs[3]; SURVEY 8d).
+256 decode rows in total sharded over N GPUs (BASELINE.json configs[3]).
 
     python benchmarks/c4_int8.py                       # 1 GPU, 256 rows
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \

@@ -130,7 +130,7 @@ def c4_int8_decode(dev, hbm_peak, B=256, T=4096, iters=6):
 
 def measured_int8_peak(dev, n=8192, iters=5):
     """What a LIBRARY int8 GEMM (cuBLASLt through torch._int_mm) reaches on this box at a large square shape: the
-    measured denominator beside the nominal 4.5 POP/s (BASELINE.md 2)."""
+    measured denominator beside the nominal 4.5 POP/s."""
     a = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8)
     b = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8)
     for _ in range(2):

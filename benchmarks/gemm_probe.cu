@@ -1,6 +1,6 @@
 // Stand-alone timing probe for gemm_i8.cu (experiments only; not part of the library).
 //   nvcc -O3 -std=c++17 -gencode arch=compute_100a,code=sm_100a -DPA_GEMM_PROBE [-DPA_GEMM_STAGES=n] \
-//        -I include -I <pkg>/csrc benchmarks/gemm_probe.cu <pkg>/csrc/page_table.cu -o gpurun_out/gemm_probe
+//        -I include -I <pkg>/csrc benchmarks/gemm_probe.cu <pkg>/csrc/page_table.cu -o gemm_probe
 #include <cstdio>
 #include <cstdlib>
 #include <vector>

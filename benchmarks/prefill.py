@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Prefill attention (SURVEY 8f row 1) timing: one layer, Llama-7B head shape (32 heads, D = 128), fp16
+"""Prefill attention timing: one layer, Llama-7B head shape (32 heads, D = 128), fp16
 and int8 pages, B prompts of Tq tokens, causal.  Reports ms per layer and achieved attention FLOP/s of the
 tensor-core flash-attention kernel (PA_PREFILL_FA=0 times the row-per-query path instead)."""
 import json

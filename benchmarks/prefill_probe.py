@@ -2,7 +2,7 @@
 """In-kernel timeline of the tcgen05 prefill kernel (csrc/prefill_tc.cu built with -DPA_PTC_PROBE).
 
     python benchmarks/prefill_probe.py --build      # here (no GPU): nvcc -> libpa_b200_probe.so, in-tree
-    gpurun -- python benchmarks/prefill_probe.py    # on the B200: run B = 2, Tq = 8192 and print the medians
+    python benchmarks/prefill_probe.py    # on a B200: run B = 2, Tq = 8192 and print the medians
 
 clock64 stamps of warp 0 (softmax group A), warp 4 (group B) and the UMMA warp over 64 steady-state KV tiles
 of CTA 5.  Softmax segments: wait S | tcgen05.ld | mask + max + exp2 + pack | wait P.V(i-1) | rescale + P

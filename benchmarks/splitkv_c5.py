@@ -1,6 +1,6 @@
 #!/usr/bin/env python
 """C5: ONE long sequence, KV pages split across the GPUs of a box, partial (m, l, O) exchanged
-over NVLink and LSE-combined (BASELINE.json configs[4]; SURVEY 8e).
+over NVLink and LSE-combined (BASELINE.json configs[4]).
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port 29533 benchmarks/splitkv_c5.py [--ctx 131072] [--check] [--iters 50]

@@ -118,8 +118,8 @@ size_t pa_decode_workspace_bytes(int B, int num_heads, int head_dim, int num_til
  * attention/paged_flash_attention_kernel_fused.cu:5-90 (launched by
  * attention/attention_tile_launcher.hpp:35-90, dispatched by
  * attention/attention_cuda.cu:41-95), with the math of
- * attention_cpu/cpu_attention_kernel.cpp:36-129 (global softmax; SURVEY App. A
- * D1-D9): for every (b, h)
+ * attention_cpu/cpu_attention_kernel.cpp:36-129 (global softmax):
+ * for every (b, h)
  *     beam   = d_beam_ids ? d_beam_ids[b] : b
  *     s[t]   = dot(q[b,h,:], K[beam,h,t,:]) / temperature      t < ctx(b)
  *     p      = exp(s - max s) / (sum exp(s - max s) + 1e-6)
@@ -370,7 +370,7 @@ int pa_linear_f32_packed(const float* d_x, const float* d_W_packed, const float*
                          int N, int act, float* d_out, void* d_workspace, size_t workspace_bytes,
                          pa_stream_t stream);
 /* logits[r,v] = dot(x[r,:], E[v,:]) against the (tied) embedding table E [vocab, hidden]
- * (SURVEY App. A D16; the reference reads logits out of the hidden state, cuda_decoder.cu:58). */
+ * (the reference reads logits out of the hidden state, cuda_decoder.cu:58). */
 int pa_logits_f32(const float* d_x, const float* d_E, int rows, int hidden, int vocab,
                   float* d_logits, pa_stream_t stream);
 int pa_logits_i8(const float* d_x, const int8_t* d_E, float qscale, int rows, int hidden, int vocab,
@@ -407,7 +407,7 @@ int pa_apply_rope_f32(float* d_q, float* d_k, const float* d_rope, const int32_t
 /* positions[r] += 1 (and ctx_lens[r] += 1 when given): advances the decode step on the device. */
 int pa_advance_positions(int32_t* d_positions, int32_t* d_ctx_lens, int rows, pa_stream_t stream);
 
-/* ------------------------------------------------ sampling (SURVEY 8f row 3) */
+/* ------------------------------------------------ sampling */
 /* attention_cpu/softmax_lut.cpp:203-231 softmax_lut_vec over vocabulary logits [rows, vocab]:
  * p = exp((x - max)/temperature) / (sum + 1e-6). */
 int pa_softmax_temperature(const float* d_logits, int rows, int vocab, float temperature, float* d_probs,
@@ -430,7 +430,7 @@ int pa_topk_topp_filter(float* d_probs, int rows, int vocab, int top_k, float to
 int pa_sample_from_probs(const float* d_probs, int rows, int vocab, const float* d_uniform,
                          int32_t* d_out_ids, pa_stream_t stream);
 
-/* ------------------------------------------------ prefill (SURVEY 8f row 1) */
+/* ------------------------------------------------ prefill */
 /* The multi-query form the reference's headers promise (q/out [B, H, T, D] and `is_prefill`,
  * attention/attention_config.hpp:8-9,17; causal rule attention/attention_kernel_utils.cuh:70-79)
  * but do not implement: query t of row b attends the cached keys [0, ctx_start[b] + t] of
@@ -519,7 +519,7 @@ int pa_splitkv_exchange_recv(void* const* d_peer_bufs, int rank, int world, int 
                              uint32_t* d_epochs, float* d_out, float* d_lse_out, int* d_status,
                              pa_stream_t stream);
 
-/* --------------------------------- NCCL form of the exchange (the north star's baseline; SURVEY 8b) */
+/* --------------------------------- NCCL form of the exchange (the north star's baseline) */
 /* NCCL is loaded at run time (dlopen "libnccl.so.2"); PA_ERR_UNSUPPORTED when it is absent.
  * pa_nccl_unique_id: rank 0 creates the 128-byte ncclUniqueId, the application distributes it;
  * pa_nccl_init: ncclCommInitRank on the current device; pa_nccl_destroy.

@@ -45,7 +45,7 @@ void* scratch(size_t need) {
 }
 
 void check(int st) {
-    if (st != PA_OK) throw std::runtime_error(pa_error_string(st));  // -> pybind11 -> RuntimeError (SURVEY 8b "Errors")
+    if (st != PA_OK) throw std::runtime_error(pa_error_string(st));  // -> pybind11 -> RuntimeError
 }
 
 }  // namespace
@@ -99,7 +99,7 @@ void AttentionCUDA::forward(const float* q, float* out, int B, int H, int D, int
                             KVTileCache<float>* kv_cache, const float* rotary_emb, bool is_prefill, bool use_fp16,
                             bool use_overlap, float temperature, int top_k, float top_p, float* rerank_scores, bool debug) {
     (void)is_prefill;  // decode form: q / out [B, H, D] (the kernels' indexing, ...fused.cu:40)
-    (void)use_fp16;    // the pool's element type decides, not a flag (SURVEY 8a row a4)
+    (void)use_fp16;    // the pool's element type decides, not a flag
     (void)debug;
     // attention_tile_launcher.hpp:48 defaults top_k to 1, which with the kernel's positional filter (...fused.cu:77)
     // would zero every key but token 0; the CPU kernel's default is "off" (cpu_attention_kernel.hpp:20).  1 = off here.

@@ -5,7 +5,7 @@
 // the buffers it has to hand to the kernels.  A maintainer adds the eight one-line const accessors below
 // (marked ADD) -- nothing else in the two headers changes.  For the compile check in tests/test_integration_stub.py this file
 // MIRRORS the declarations of the two reference classes member for member (same names, same order, same types;
-// method bodies omitted because they do not compile as shipped, SURVEY App. C) and adds the accessors.
+// method bodies omitted because they do not compile as shipped) and adds the accessors.
 #pragma once
 #include <list>
 #include <mutex>

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """TEST INFRASTRUCTURE ONLY -- build the reference's OWN cpu_paged_attention_forward into oracle/_ref.
 
-attention_cpu/cpu_attention_kernel.cpp does not compile as shipped (SURVEY App. C): the struct
+attention_cpu/cpu_attention_kernel.cpp does not compile as shipped: the struct
 member / local `int T` shadows the template parameter `T`, `Vec` is used before any
 using-declaration and with a 2-argument load/store that vec_cpu.hpp does not have, and
 `kv_cache->get` is called with a fourth 'k'/'v' argument KVTileCacheCPU does not take.  This

@@ -26,7 +26,7 @@ _u8p = C.POINTER(C.c_uint8)
 
 
 def build(force=False):
-    """Compile oracle_cpu.c (and, when /root/reference exists, oracle/_ref)."""
+    """Compile oracle_cpu.c (and, when the reference tree exists, oracle/_ref)."""
     if force or not os.path.exists(_LIB_PATH):
         subprocess.check_call(["make", "-C", _HERE, "oracle"], stdout=subprocess.DEVNULL)
     ref_so = os.path.join(_HERE, "_ref", "libref_cpu.so")

@@ -2,7 +2,7 @@
 pinned pieces.  Every STAGE is pinned bit-exact against the reference's own compiled code
 (embedding lookup, LayerNorm<float>, MLP<float>, cpu_paged_attention_forward<float>, int8_quant:
 tests/test_oracle_pinning.py); the WIRING between them is not: decoder_block.hpp / cuda_decoder.cu /
-int8_decoder.cpp do not compile and never append K/V (SURVEY G7, App. A D16), so this file restates the
+int8_decoder.cpp do not compile and never append K/V, so this file restates the
 decisions llm_decoder/decoders.py documents, step by step, as an independent CPU path.
 
   decoder/token_embedding.hpp:19-26  embedding lookup

@@ -5,7 +5,7 @@
  * tiled KV cache, page-table gather/append addressing, INT8 quantise /
  * dequantise, LUT softmax family, s8 x s8 -> s32 matmul with the oneDNN-style
  * epilogue).  Every function cites the reference file:line it follows
- * (paths relative to /root/reference).
+ * (paths relative to the reference tree).
  *
  * Only tests/, __graft_entry__.smoke() and bench.py's cpu_baseline /
  * --impl reference legs may load this.  The product path (libpa_b200.so) never
@@ -14,12 +14,12 @@
  * Parity pinning: the int8_quant, softmax_lut and KVTileCacheCPU restatements
  * are pinned bit-for-bit against the reference's own objects (oracle/_ref,
  * built from the unmodified reference sources) in tests/test_oracle_pinning.py
- * and against SURVEY.md Appendix B known answers.  The attention restatement
- * follows cpu_attention_kernel.cpp, which does not compile as shipped
- * (SURVEY.md App. C); its softmax / filter stages are pinned against the
+ * and against hand-computed known answers.  The attention restatement
+ * follows cpu_attention_kernel.cpp, which does not compile as shipped;
+ * its softmax / filter stages are pinned against the
  * reference objects, its loop structure is a line-by-line restatement.
  * The oneDNN epilogue is "parity unpinned" (third-party, un-vendored,
- * un-pinned oneDNN < 3.0; see DESIGN.md): only the int32 accumulators are a
+ * un-pinned oneDNN < 3.0): only the int32 accumulators are a
  * bit-exact target.
  *
  * Build: gcc -O2 -fopenmp -ffp-contract=off -fno-fast-math (see oracle/Makefile).
@@ -57,7 +57,7 @@ ORC_API int orc_pt_lookup(const int32_t* table, int total_entries, int beam, int
 
 /* kv_cache/kv_tile_cache.hpp:21-26  KVTileCache<T>::get address math.
  * Returns the ELEMENT offset of the page start in the K (or V) pool, or -1
- * for "nullptr".  64-bit offset (SURVEY App. A D17). */
+ * for "nullptr".  64-bit offset. */
 ORC_API int64_t orc_kv_page_offset(const int32_t* table, int total_entries, int beam,
                                    int head, int tile, int num_heads, int num_tiles,
                                    int total_pages, int tile_size, int head_dim) {
@@ -88,7 +88,7 @@ ORC_API void orc_gather_pages(const uint8_t* pool, uint8_t* dense, const int32_t
     }
 }
 
-/* KV append: the reference has no append (SURVEY G7); the storage layout and
+/* KV append: the reference has no append; the storage layout and
  * get_write_ptr (kv_tile_cache.hpp:29-34) define it: the row of token `pos`
  * lives at page(beam,head,pos/tile_size) + (pos % tile_size)*head_dim.
  * new_k/new_v: [R, H, D] elements of elem_bytes.  Rows whose page is unmapped
@@ -103,7 +103,7 @@ ORC_API void orc_kv_append(uint8_t* k_pool, uint8_t* v_pool, const int32_t* tabl
     for (int r = 0; r < R; ++r) {
         int beam = beam_ids ? beam_ids[r] : r;
         int pos = positions[r];
-        /* deliberate deviation (SURVEY App. A D14 family): a position past the table's capacity, or a beam outside
+        /* deliberate deviation: a position past the table's capacity, or a beam outside
          * it, writes nothing; the reference's flat-index bound (page_table.hpp:44-49) would alias into another
          * head's / beam's entry and overwrite its page. */
         if (pos < 0 || pos / tile_size >= num_tiles || beam < 0 || beam >= num_beams) continue;
@@ -196,7 +196,7 @@ ORC_API float orc_compute_minmax_scale(const float* x, int64_t n) {
 }
 
 /* Row-wise minmax scale: one scale per row of `dim` (the per-(token,head)
- * granularity used for the INT8 KV cache; SURVEY 8a a9). */
+ * granularity used for the INT8 KV cache). */
 ORC_API void orc_batch_minmax_scale(const float* x, int rows, int dim, float* scales) {
     for (int b = 0; b < rows; ++b) scales[b] = orc_compute_minmax_scale(x + (int64_t)b * dim, dim);
 }
@@ -239,7 +239,7 @@ ORC_API void orc_fused_softmax_lut(const int32_t* logits, int64_t n, float scale
 
 /* softmax_lut.cpp:21-57 softmax_lut (8-wide Vec form: sum accumulated as
  * per-chunk partial sums).  n must be a multiple of 8 (the reference overruns
- * otherwise, SURVEY App. C). */
+ * otherwise). */
 ORC_API void orc_softmax_lut(const int32_t* logits, int64_t n, float scale, const float* lut,
                              int resolution, float* out) {
     const float max_x = 10.0f;
@@ -378,7 +378,7 @@ static inline void orc_load_row(float* dst, const void* pool, const float* scale
  * table: dense int32 [num_beams][H][num_tiles], -1 = unmapped.
  * ctx_lens: per-row T (NULL -> T for every row; the reference has one T).
  * double_temperature: reproduce the CPU path's second division by
- *   temperature inside softmax_lut_vec (SURVEY App. A D3); 0 = GPU semantics.
+ *   temperature inside softmax_lut_vec; 0 = GPU semantics.
  * probs_out / logits_out: optional [B, H, T] (CPUAttentionOutput, hpp:34-39).
  */
 ORC_API void orc_paged_attention(const float* q, float* out, const void* k_pool,

@@ -1,10 +1,10 @@
 """TEST INFRASTRUCTURE ONLY -- wrappers over oracle/_ref/libref_cpu.so.
 
 That library is the reference's OWN int8_quant.cpp, softmax_lut.cpp and
-kv_tile_cache_cpu.cpp, compiled unmodified from /root/reference by oracle/Makefile
+kv_tile_cache_cpu.cpp, compiled unmodified from the reference tree by oracle/Makefile
 (plus oracle/ref_shim.cpp, which only adapts std::vector signatures).  It is git-ignored
-but travels to the GPU box with the gpurun snapshot.  `available()` is False when it has
-not been built (no /root/reference and no prebuilt .so).
+but is used where it has been built.  `available()` is False when it has
+not been built (no the reference tree and no prebuilt .so).
 """
 import ctypes as C
 import os

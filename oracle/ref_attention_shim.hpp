@@ -1,7 +1,7 @@
 // ref_attention_shim.hpp -- TEST INFRASTRUCTURE ONLY.
 //
 // The two helper types attention_cpu/cpu_attention_kernel.cpp:36-129 is written against but
-// the reference never defines (SURVEY App. C): a D-element float vector with 2-argument
+// the reference never defines: a D-element float vector with 2-argument
 // load/store ("will decode if int8_t", cpu_attention_kernel.cpp:52-53, 80, 120) and a tile
 // store whose `get` takes a fourth 'k'/'v' argument (cpu_attention_kernel.cpp:72, 107).
 // They carry no arithmetic of their own: load/store are element-wise casts, the store

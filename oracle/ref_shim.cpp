@@ -1,9 +1,9 @@
 // ref_shim.cpp -- TEST INFRASTRUCTURE ONLY.
 //
 // extern "C" trampolines over the reference's OWN translation units that
-// compile as shipped (SURVEY.md G2): attention_cpu/int8_quant.cpp,
+// compile as shipped: attention_cpu/int8_quant.cpp,
 // attention_cpu/softmax_lut.cpp (-fpermissive) and kv_cache/kv_tile_cache_cpu.cpp.
-// The reference sources are compiled where they lie under /root/reference by
+// The reference sources are compiled where they lie under the reference tree by
 // oracle/Makefile into oracle/_ref/libref_cpu.so; nothing is copied into this
 // repo.  This file only adapts std::vector signatures to plain pointers so
 // Python (ctypes) can call them.  Used to pin oracle_cpu.c and, in bench.py's

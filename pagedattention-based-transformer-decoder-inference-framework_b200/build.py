@@ -2,7 +2,7 @@
 
     python build.py [--force] [--verbose] [--core]
 
-The .so lands next to csrc/ (git-ignored, but it travels to the GPU box with gpurun).
+The .so lands next to csrc/ (git-ignored).
 
 --core builds libpa_b200_core.so from the CORE sources only: the page table, the small decoder ops with the fp32 linear
 layer, sampling, and the ragged-batch sequence ops (norm / token shift / recurrence, differential and latent attention,

@@ -11,7 +11,7 @@
 // paged_decode.cu; it is the explicit three-stage form, for the callers that ask for filtering or the side outputs
 // (defaults top_k = 0, top_p = 1 keep the hot path).  Softmax and filter are the kernels of sampling.cu
 // (pa_softmax_temperature, pa_topk_topp_filter: radix select with the reference's tie order).
-// The temperature is applied ONCE (SURVEY App. A D3), as in the hot path.
+// The temperature is applied ONCE, as in the hot path.
 #include "pa_common.cuh"
 
 extern "C" int pa_softmax_temperature(const float*, int, int, float, float*, pa_stream_t);

@@ -1,6 +1,6 @@
 // decoder_ops.cu -- the small device ops that keep CUDADecoder / INT8Decoder.generate on the
-// GPU between two attention calls ("minimal GPU versions only to keep
-// generate end-to-end"): token embedding, LayerNorm, the fp32 MLP linear layers, tied-embedding
+// GPU between two attention calls (minimal GPU versions, only to keep generate
+// end-to-end): token embedding, LayerNorm, the fp32 MLP linear layers, tied-embedding
 // logits and greedy argmax.  All are HBM-bound streaming kernels at decode batch sizes (a few
 // rows against a weight matrix read exactly once).
 //

@@ -180,7 +180,7 @@ __device__ __forceinline__ uint32_t epilogue_s8(int acc, float alpha, float bias
 // floor(|y| + 0.5) with the sign put back.  The addition is done round-TOWARD-ZERO, which makes it exact where it
 // matters: RZ(|y| + 0.5) >= n exactly when |y| + 0.5 >= n for every integer n (n is representable), so truncating it
 // gives floor(|y| + 0.5) -- e.g. 0.49999997 + 0.5 stays below 1 (round-to-nearest would give 1.0 and the wrong answer;
-// SURVEY App. B has that value).  cvt.rzi.sat truncates and saturates to [-128, 127] in one instruction.
+// the known-answer tests have that value).  cvt.rzi.sat truncates and saturates to [-128, 127] in one instruction.
 __device__ __forceinline__ uint32_t quantize_half_away_s8(float y) {
     const float half = __uint_as_float((__float_as_uint(y) & 0x80000000u) | 0x3f000000u);  // copysign(0.5, y)
     uint32_t q;

@@ -1,4 +1,4 @@
-// p2p_combine.cu -- inter-GPU split-KV combine (north-star long-context mode, SURVEY 8e).  The reference has
+// p2p_combine.cu -- inter-GPU split-KV combine (north-star long-context mode).  The reference has
 // no multi-device code; the exchange step is new.
 //
 // Each rank holds a contiguous page range of ONE sequence and produces un-normalised partials (m, l, O) per
@@ -176,7 +176,7 @@ PA_API int pa_splitkv_exchange_recv(void* const* d_peer_bufs, int rank, int worl
                            d_status, stream, 2);
 }
 
-// ---- NCCL form (SURVEY 8b "pa_nccl_* init / allgather-combine", 8e) ---------------------------------------
+// ---- NCCL form ---------------------------------------
 PA_API int pa_nccl_unique_id(unsigned char* id128) {
     PA_CHECK_ARG(id128);
     NcclApi& n = nccl();

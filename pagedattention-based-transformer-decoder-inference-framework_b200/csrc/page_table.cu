@@ -39,7 +39,7 @@ __device__ __forceinline__ int pt_lookup(const int32_t* __restrict__ table, int6
                                          int num_tiles) {
     // The reference computes the flat index in 32-bit int (page_table.hpp:41); out-of-range
     // components therefore alias into other rows.  We keep the flat-index bounds check
-    // (idx < 0 || idx >= total) and do the arithmetic in 64 bit (SURVEY App. A D17).
+    // (idx < 0 || idx >= total) and do the arithmetic in 64 bit.
     int64_t idx = (int64_t)beam * ((int64_t)num_heads * num_tiles) + (int64_t)head * num_tiles + tile;
     if (idx < 0 || idx >= total_entries) return -1;
     return table[idx];

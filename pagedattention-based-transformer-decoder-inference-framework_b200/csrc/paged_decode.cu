@@ -2,7 +2,7 @@
 //
 // Replaces attention/paged_flash_attention_kernel_fused.cu:5-90 (a1) and
 // attention/paged_flash_attention_kernel_fused_overlap.cu:5-91 (a2) with the math of
-// attention_cpu/cpu_attention_kernel.cpp:36-129 (global softmax; SURVEY App. A D1-D9).
+// attention_cpu/cpu_attention_kernel.cpp:36-129 (global softmax).
 //
 // The op is HBM-bound (~1 flop/B): every K/V byte is read once.  Design:
 //   * the unit of work is a 16-token sub-tile of one page: K [16][D] + V [16][D],

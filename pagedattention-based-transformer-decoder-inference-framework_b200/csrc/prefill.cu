@@ -1,5 +1,5 @@
-// prefill.cu -- multi-query (prefill / chunked-prefill) attention over the paged KV cache:
-// SURVEY 8(f) row 1.  The reference's headers promise it -- q/out laid out [B, H, T, D] and an
+// prefill.cu -- multi-query (prefill / chunked-prefill) attention over the paged KV cache.
+// The reference's headers promise it -- q/out laid out [B, H, T, D] and an
 // `is_prefill` flag (attention/attention_config.hpp:8-9,17), causal mask helper
 // attention/attention_kernel_utils.cuh:70-79 (key_pos > query_pos is masked) -- but ship no code.
 //

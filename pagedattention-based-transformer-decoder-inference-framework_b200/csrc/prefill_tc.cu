@@ -1,5 +1,5 @@
 // prefill_tc.cu -- flash-attention prefill over the paged cache on the 5th-generation tensor cores
-// (tcgen05.mma kind::f16, accumulators in TMEM), fp16 and int8 pages, head_dim 64 / 128.  SURVEY 8(f) row 1.
+// (tcgen05.mma kind::f16, accumulators in TMEM), fp16 and int8 pages, head_dim 64 / 128.
 //
 // One CTA = 256 consecutive query positions of one (row, head), handled as TWO query tiles of 128 rows
 // (A, B) that share every K/V tile; KV is consumed in tiles of 64 tokens (4 page units of 16 tokens, each

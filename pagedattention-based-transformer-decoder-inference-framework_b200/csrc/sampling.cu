@@ -1,5 +1,5 @@
 // sampling.cu -- temperature softmax, top-k / top-p filter with the EOS rule, and inverse-CDF
-// sampling over vocabulary logits on the device (SURVEY 8f row 3).
+// sampling over vocabulary logits on the device.
 //
 //   attention_cpu/softmax_lut.cpp:203-231  softmax_lut_vec: p = exp((x - max)/T) / (sum + 1e-6)
 //   attention_cpu/softmax_lut.cpp:233-256  apply_topk_topp_filter: sort (prob, index) pairs descending

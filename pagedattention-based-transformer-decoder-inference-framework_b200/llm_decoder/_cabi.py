@@ -180,7 +180,7 @@ EXPORTS = tuple(_SIGS)
 
 class PAError(RuntimeError):
     """A non-zero status from libpa_b200.so (mirrors the reference's C++ exception ->
-    pybind11 -> RuntimeError path, SURVEY 8b 'Errors')."""
+    pybind11 -> RuntimeError path)."""
 
 
 def _missing(name, path):

@@ -3,7 +3,7 @@ libpa_b200.so.
 
 Mirrors attention/attention_config.hpp:5-26 (`AttentionCUDA::forward`, 17 positional
 arguments, same names and order) and attention/attention_tile_launcher.hpp:35-90.
-Differences that are decisions (SURVEY App. A): the KV storage dtype comes from the
+Differences that are decisions: the KV storage dtype comes from the
 `kv_cache` object, not from runtime heuristics on temperature/top_k (D-a4); softmax is
 global over the context (D1); `out` is overwritten (D9); in-attention top-k/top-p is
 rejected unless disabled (D6; the launcher default top_k=1 would zero every key but one);

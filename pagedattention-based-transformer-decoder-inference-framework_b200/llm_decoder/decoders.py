@@ -6,7 +6,7 @@ returning prompt + generated ids.
 The layer loop is the reference's (decoder/decoder_block.hpp:41-62): LN1 -> attention (q := LN1
 output, B=1 per sequence, no QKV/O projections, no residuals) -> LN2 -> MLP(ReLU, 4x hidden,
 decoder/mlp.hpp:23-41), greedy argmax sampling (cuda_decoder.cu:7-14 / int8_decoder.cpp:97-104).
-Decisions where the reference is not well defined (SURVEY App. A D16), stated here because
+Decisions where the reference is not well defined, stated here because
 token-level parity with a program that never appends K/V and recomputes the whole sequence on
 the host with aliased buffers is meaningless:
   * decode is incremental: each step appends the new token's K/V rows (K = V = the LN1 output
@@ -20,7 +20,7 @@ the host with aliased buffers is meaningless:
     dnnl_matmul_int8 -> dequant" pipeline of attention_cpu/README.md:80-86 instead of
     MLP<int8_t>'s overflowing int8 accumulators (mlp.hpp:28).
 
-Optional attention projections (weights/README.md:31-34): when a layer directory holds
+Optional attention projections: when a layer directory holds
 attn_wq.bin / attn_wk.bin / attn_wv.bin / attn_wo.bin (each [hidden, hidden] row-major, column block h = head h's
 [hidden, head_dim] matrix of the README), q = n.Wq, k = n.Wk, v = n.Wv feed the paged cache / attention and the
 attention output is multiplied by Wo before LN2.  CUDADecoder: fp32 (pa_linear_f32); INT8Decoder: int8 weights on the
@@ -250,7 +250,7 @@ class _DecoderBase:
                                                  _cabi.stream()), "pa_advance_positions")
 
     def _prefill(self, prompt):
-        """All prompt tokens of all sequences in ONE pass through the stack (SURVEY 8f row 1): row
+        """All prompt tokens of all sequences in ONE pass through the stack: row
         (b, t) appends its K/V at position t of table row b and attends causally (ctx = t + 1) through
         the beam indirection of the decode kernels; LayerNorm and the MLP GEMMs run on B*n rows.
         Leaves the first sampled token in self.ids and positions = n."""
@@ -316,7 +316,7 @@ class _DecoderBase:
                        eos_thresh=0.0, seed=None):
         """Decode several sequences at once (equal prompt lengths): rows are independent.  Greedy argmax (the
         reference's sampler) unless top_k > 0 or top_p < 1, which switch to temperature / top-k / top-p / EOS
-        sampling on the device (SURVEY 8f row 3) with a torch generator seeded by `seed`."""
+        sampling on the device with a torch generator seeded by `seed`."""
         B = len(prompts)
         n_prompt = len(prompts[0])
         if n_prompt == 0 or any(len(p) != n_prompt for p in prompts):

@@ -1,6 +1,6 @@
 """Multi-GPU modes of the decode hot path (one process per GPU, torch.distributed / NCCL).
 
-The reference has no multi-device code at all (SURVEY G4); BASELINE.json's north star adds two
+The reference has no multi-device code at all; BASELINE.json's north star adds two
 modes, both implemented here:
 
 * batch sharding -- rows (sequences) are independent (grid(B,H), attention_tile_launcher.hpp:53),

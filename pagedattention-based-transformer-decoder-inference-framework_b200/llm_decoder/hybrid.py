@@ -900,7 +900,8 @@ class HybridDecoder:
                                self._gain1p(W["final.norm"]) if pre else None)
         if self.final_gain_vec is not None and self.final_gain_vec.numel() != self.width:
             raise ValueError("final.norm does not match width")
-        self.logit_scale, self.logit_softcap = float(config.get("logit_scale", 1.0)), float(config.get("logit_softcap", 0.0))
+        ls, lc_ = config.get("logit_scale"), config.get("logit_softcap")      # absent or null: no scaling / no cap
+        self.logit_scale, self.logit_softcap = 1.0 if ls is None else float(ls), 0.0 if lc_ is None else float(lc_)
         mixers = self.design.get("mixers") or {k: (v, {}) for k, v in MIXERS.items()}
         self.layers = []
         for i, lc in enumerate(config["layers"]):

@@ -11,7 +11,7 @@ than one map, or whose values are wider than its keys); the per-request lifecycl
 `register_tile` as tokens arrive and `release_beam` when the request ends, with `evict_on_exhaustion = False`
 so that a full pool is an error instead of the silent loss of a live request's oldest tile.
 
-Decisions taken where the reference contradicts itself (SURVEY App. A D14): page ids come
+Decisions taken where the reference contradicts itself: page ids come
 from a free list (the reference's `map.size()` re-issues live ids after an eviction),
 eviction clears the device entry, and the page-table dimensions are given explicitly with
 `configure_table(num_beams, num_heads, num_tiles)` (the reference passes
@@ -237,7 +237,7 @@ class KVTileCache:
     # ---- GPU <-> CPU tile offload in the reference's CPU tile-store format --------------------
     # KVTileCacheCPU<T>::save / load (kv_cache/kv_tile_cache_cpu.cpp:89-123): int32 count, then per tile
     # {TileIndex = 3 x int32 (batch, head, tile), tile_size x T payload}.  The CPU store has no K/V
-    # distinction (SURVEY a13), so a tile's payload here is its K page followed by its V page (int8
+    # distinction, so a tile's payload here is its K page followed by its V page (int8
     # caches append the two f32 scale rows); the file can be loaded by the reference's own
     # KVTileCacheCPU with tile_size = tile_payload_bytes() / sizeof(T).
     def tile_payload_bytes(self):

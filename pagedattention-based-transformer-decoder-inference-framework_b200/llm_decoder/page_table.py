@@ -1,7 +1,7 @@
 """PageTable -- dense device-resident int32 map [num_beams][num_heads][num_tiles] -> page id.
 
 Mirrors kv_cache/page_table.hpp:5-49 / page_table.cpp:6-67 (same method names and
-argument meaning).  Differences that are decisions, not accidents (SURVEY App. A D14):
+argument meaning).  Differences that are decisions, not accidents:
 `assign`/`remove` update a host mirror and are flushed to the device in ONE batched
 kernel (pa_page_table_update) instead of one blocking 4-byte cudaMemcpy per entry, and
 `sync_to_gpu` uploads the mirror WITH the assignments (the reference's mirror never sees

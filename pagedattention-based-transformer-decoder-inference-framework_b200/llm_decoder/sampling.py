@@ -1,4 +1,4 @@
-"""Device-side sampling over vocabulary logits (SURVEY 8f row 3): the reference's CPU filters
+"""Device-side sampling over vocabulary logits: the reference's CPU filters
 (attention_cpu/softmax_lut.cpp:203-256) and its GPU sketch (attention/top_k_top_p_filter.cuh:55-111)
 as three kernels of libpa_b200.so.  Tensors are CUDA float32 [rows, vocab]."""
 import torch

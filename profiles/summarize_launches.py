@@ -2,7 +2,7 @@
 total / share (the SHARE of the step is what must agree with bench.py's live CUDA-event timing;
 ncu's per-launch times are cold-cache and serialised).
 
-    python profiles/summarize_launches.py gpurun_out/launches.csv > profiles/<name>.txt
+    python profiles/summarize_launches.py launches.csv > profiles/<name>.txt
 """
 import collections
 import csv

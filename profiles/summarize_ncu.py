@@ -1,6 +1,6 @@
-"""Summarise an .ncu-rep (read here, no GPU) into the handful of counters DESIGN.md cites.
+"""Summarise an .ncu-rep (read here, no GPU) into a handful of counters.
 
-    python profiles/summarize_ncu.py gpurun_out/prof.ncu-rep > profiles/<name>.txt
+    python profiles/summarize_ncu.py prof.ncu-rep > profiles/<name>.txt
 """
 import csv
 import io

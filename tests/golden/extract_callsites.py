@@ -1,6 +1,6 @@
 """Extract the SHAPE of every decoder call site in the reference's Python callers (api/, cli/, web/):
 file, line, callee, positional-argument kinds, keyword names -- no source text.  Run in the build
-container (needs /root/reference):
+container (needs the reference tree):
 
     python tests/golden/extract_callsites.py
 

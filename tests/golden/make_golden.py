@@ -1,6 +1,6 @@
 """Generate tests/golden/ref_vectors.npz by RUNNING the reference's own objects
-(oracle/_ref/libref_cpu.so = unmodified /root/reference int8_quant.cpp, softmax_lut.cpp,
-kv_tile_cache_cpu.cpp).  Run in the build container (needs /root/reference):
+(oracle/_ref/libref_cpu.so = the reference's unmodified int8_quant.cpp, softmax_lut.cpp,
+kv_tile_cache_cpu.cpp).  Run in the build container (needs the reference tree):
 
     python tests/golden/make_golden.py
 

@@ -1,4 +1,4 @@
-"""Seeded synthetic inputs for the paged-decode hot path (SURVEY.md 8d).
+"""Seeded synthetic inputs for the paged-decode hot path.
 
 Generated on the CPU so the oracle and the kernels see identical bits: q, K, V ~ N(0,1)
 with K/V rounded to fp16 (or quantised with the int8_quant oracle), page ids a random

@@ -1,8 +1,8 @@
-"""Out-of-bounds WRITE detection with guard zones (compute-sanitizer is closed on this pool: "find a bad access with
-bounds checks and asserts of your own").  Every buffer a kernel writes -- outputs, side outputs, and the scratch
+"""Out-of-bounds WRITE detection with guard zones (a stand-in for a memory checker where none
+can run).  Every buffer a kernel writes -- outputs, side outputs, and the scratch
 whose size the library itself reports -- is carved out of the middle of a poisoned arena with 16 KiB of canaries on
 each side, at EXACTLY the size the API asks for; after the kernel the canaries must be intact.  Run over the hand-rolled
-pipelines the VERDICT names: the streaming decode kernels (mbarrier rings, chunk partials, in-kernel row merge), the
+pipelines: the streaming decode kernels (mbarrier rings, chunk partials, in-kernel row merge), the
 split-KV grid kernel + merge kernels, the beam-group kernel, the tcgen05 GEMM (direct, split-K scratch, fused
 dynamic-quantisation epilogue), the tcgen05 prefill, the row append and the exchange.  Results are also checked against
 the oracle, so a kernel cannot pass by writing nothing."""

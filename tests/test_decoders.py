@@ -1,4 +1,4 @@
-"""Decoder surface (SURVEY 8a row a14, 8b): CUDADecoder / INT8Decoder constructor, weight files,
+"""Decoder surface: CUDADecoder / INT8Decoder constructor, weight files,
 generate() -- checked against the CPU restatement oracle/decoder_ref.py with teacher forcing
 (token-level equality is only asserted where the oracle's own top-2 margin exceeds the numeric
 noise), plus the small decoder kernels one by one."""

@@ -1,4 +1,4 @@
-"""Multi-GPU host logic on CPU: world_size-2 gloo process group (SURVEY 8e).  The device kernels
+"""Multi-GPU host logic on CPU: world_size-2 gloo process group.  The device kernels
 are replaced by the oracle here, only to verify the exchange plumbing (partials computed by
 the oracle over each rank's page range, packed, all-gathered, combined)."""
 import os

@@ -3,8 +3,8 @@ ctypes layer), against the CPU oracle on the same seeded inputs.
 
 Bars (BASELINE.json north_star): page-table gather/append and INT8 quantise/dequantise are
 BIT-EXACT; float attention output within 2e-3 relative / 1e-3 absolute of the oracle fed the
-same fp16-rounded K/V; the INT8-KV path within the LUT-softmax envelope (0.03*max|V|, SURVEY
-App. B) -- in practice it meets the float bar too, which is what we assert.
+same fp16-rounded K/V; the INT8-KV path within the LUT-softmax envelope (0.03*max|V|) --
+in practice it meets the float bar too, which is what we assert.
 """
 import os
 
@@ -199,7 +199,7 @@ def test_decode_matches_oracle(ld, oracle, ci, kv, overlap):
     got, lse = run_decode(ld, case, overlap)
     assert np.isfinite(got).all()
     np.testing.assert_allclose(got, exp, rtol=RTOL, atol=ATOL)
-    # LUT-softmax envelope for the INT8 path (SURVEY App. B) -- far looser than the above
+    # LUT-softmax envelope for the INT8 path -- far looser than the above
     if kv == "i8":
         vmax = np.abs(case["v_pool"].astype(np.float32) / case["v_scales"][..., None]).max()
         assert np.abs(got - exp).max() <= 0.03 * vmax
@@ -372,7 +372,7 @@ def test_host_pipe_async_forward_matches_device(ld, oracle):
     assert torch.equal(kvc.key_buffer_, kvc2.key_buffer_) and torch.equal(kvc.value_buffer_, kvc2.value_buffer_)
 
 
-# ------------------------------------------------------------------ page lifecycle (SURVEY 8f row 2)
+# ------------------------------------------------------------------ page lifecycle
 @pytest.mark.parametrize("kv", ["f16", "i8"])
 def test_tile_offload_in_reference_cpu_format(ld, oracle, kv, tmp_path):
     """save_tiles_cpu_format writes the layout of KVTileCacheCPU<T>::save (kv_tile_cache_cpu.cpp:89-103):
@@ -413,7 +413,7 @@ def test_tile_offload_in_reference_cpu_format(ld, oracle, kv, tmp_path):
         kvc2.load_tiles_cpu_format(str(tmp_path / "nope.bin"))
 
 
-# ------------------------------------------------------------------ prefill (SURVEY 8f row 1)
+# ------------------------------------------------------------------ prefill
 @pytest.mark.parametrize("kv", ["f16", "i8"])
 def test_prefill_causal_matches_oracle(ld, oracle, kv):
     """q/out [B, H, Tq, D]; query t of row b sees keys [0, ctx_start[b] + t] (causal rule of
@@ -961,7 +961,7 @@ def test_gemm_i8_rejects_bad_shapes(ld):
 @pytest.mark.parametrize("shape", [(256, 16384, 4096), (256, 4096, 16384)], ids=["C4_fc1", "C4_fc2"])
 def test_gemm_i8_c4_full_size_vs_onednn(ld, shape):
     """BASELINE config C4 MLP shapes; exact int32 accumulators against oneDNN's s8 GEMM on the
-    host (torch._int_mm on CPU tensors = the only linkable oneDNN here, SURVEY 8d)."""
+    host (torch._int_mm on CPU tensors = the only linkable oneDNN here)."""
     M, N, K = shape
     g = torch.Generator().manual_seed(1238)
     A = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8)

@@ -1,6 +1,6 @@
 """The C++ binding INTEGRATION.md describes is real code: integration/attention_cuda_b200.cpp compiles (g++ -std=c++17
 -Wall -Werror) against include/pa_b200.h and the mirrored reference declarations of integration/ref_accessors.hpp, and
-links against libpa_b200.so (every pa_* symbol it calls exists with that arity).  When /root/reference is present the
+links against libpa_b200.so (every pa_* symbol it calls exists with that arity).  When the reference tree is present the
 mirror is checked against the reference's own headers: every member it declares is a member of the reference class."""
 import os
 import re
@@ -33,7 +33,7 @@ def test_stub_compiles_and_links(tmp_path):
 
 def test_mirror_matches_reference_headers():
     if not os.path.exists("/root/reference/kv_cache/page_table.hpp"):
-        pytest.skip("no /root/reference")
+        pytest.skip("no the reference tree")
     mirror = open(MIRROR).read()
     for hdr, cls in (("kv_cache/page_table.hpp", "PageTable"), ("kv_cache/kv_tile_cache.hpp", "KVTileCache")):
         ref = open(os.path.join("/root/reference", hdr)).read()

@@ -1,8 +1,8 @@
-"""Page lifecycle (SURVEY 8f row 2): the host logic either side of gather/append.
+"""Page lifecycle: the host logic either side of gather/append.
 
 kv_cache/kv_tile_cache.cpp:27-37 (resize), :65-98 (register_tile, LRU, evict_if_needed), :105-125
-(save_to_file / load_from_file: raw K pool then raw V pool, no header) -- with the decisions of SURVEY App. A
-D14 (free-list page ids, eviction clears the device entry) and the copy-on-write refcounts of the beam path:
+(save_to_file / load_from_file: raw K pool then raw V pool, no header) -- with these decisions
+(free-list page ids, eviction clears the device entry) and the copy-on-write refcounts of the beam path:
 a page shared by several beams is returned to the free list only when its LAST reference is released.
 """
 import os

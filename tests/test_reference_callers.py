@@ -1,9 +1,9 @@
-"""SURVEY 8(f) row 4 / 8(b) "caller-side variants": the reference's Python callers (api/, cli/, web/) against
+"""Caller-side variants: the reference's Python callers (api/, cli/, web/) against
 the new `llm_decoder`, unmodified.
 
 * tests/golden/ref_callsites.json holds the SHAPE of every decoder call site in those files (extracted with
   `ast` by tests/golden/extract_callsites.py: callee, positional kinds, keyword names, literal values).
-* CPU: the fixture is current (when /root/reference is present), every call shape binds to the real signatures,
+* CPU: the fixture is current (when the reference tree is present), every call shape binds to the real signatures,
   the argument normalisation of `generate` maps each form to (prompt, out-list, max_len, temperature), the
   import-path shim resolves `from decoder.cuda_decoder import CUDADecoder`, and api/router.py itself is executed
   UNMODIFIED with only its out-of-scope collaborators stubbed (tokenizer, reranker) and the device loop of the
@@ -43,7 +43,7 @@ def _generate_args(site, prompt, out_list, max_tokens, temperature):
 
 def test_callsite_fixture_is_current():
     if not os.path.exists(os.path.join(REF, "api", "router.py")):
-        pytest.skip("no /root/reference")
+        pytest.skip("no the reference tree")
     sys.path.insert(0, os.path.join(HERE, "golden"))
     try:
         import extract_callsites
@@ -124,10 +124,10 @@ class _Recorder:
 
 
 def test_reference_api_router_runs_unmodified():
-    """Execute /root/reference/api/router.py as shipped.  Stubbed: api.tokenizer (downloads GPT-2), reranker.reranker
-    (out of scope, SURVEY 2), and the decoder's device loop (no GPU here)."""
+    """Execute the reference's api/router.py as shipped.  Stubbed: api.tokenizer (downloads GPT-2), reranker.reranker
+    (out of scope), and the decoder's device loop (no GPU here)."""
     if not os.path.exists(os.path.join(REF, "api", "router.py")):
-        pytest.skip("no /root/reference")
+        pytest.skip("no the reference tree")
     pytest.importorskip("fastapi")
     from llm_decoder.decoders import _DecoderBase
     rec = type("CUDADecoder", (_Recorder,), {"generate": _DecoderBase.generate,

@@ -1,4 +1,4 @@
-"""Device sampling kernels (SURVEY 8f row 3) against the oracle restatement of
+"""Device sampling kernels against the oracle restatement of
 attention_cpu/softmax_lut.cpp:203-256, which is itself pinned bit-exactly against the reference's
 own object (tests/test_oracle_pinning.py)."""
 import numpy as np
@@ -82,7 +82,7 @@ def test_topk_topp_filter_matches_oracle(ld, oracle):
         _filter_case(ld, oracle, p, 0, 1.0, eos, 0.0)            # EOS rule fires (prob > 0)
         _filter_case(ld, oracle, p, 0, 1.0, eos, 0.9)            # does not fire
         _filter_case(ld, oracle, p, 2, 1.0, int(np.argmax(p[2])), 1e-6)
-    # SURVEY App. B known answers
+    # hand-computed known answers
     kv = np.array([[0.1, 0.4, 0.2, 0.3]], np.float32)
     for tk, tp in ((2, 1.0), (0, 0.6)):
         got = ld.sampling.apply_topk_topp_filter(torch.from_numpy(kv.copy()).cuda(), tk, tp).cpu().numpy()
